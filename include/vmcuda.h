@@ -16,6 +16,12 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#if defined(__GNUC__)
+#define VM_API __attribute__((visibility("default")))
+#else
+#define VM_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -108,17 +114,17 @@ enum {
  * layers_per_group[g] of them belong to ConvolutionalGroup g (cpp/visualmesh/network_structure.hpp:47-52): the first
  * layer of a group consumes the (N+1)-row gather, the others follow without one. n_groups == 0 gives a
  * projection-only engine. device < 0 selects the current device. */
-vm_status vm_engine_create(int device,
+VM_API vm_status vm_engine_create(int device,
                            const vm_layer* layers,
                            const int32_t* layers_per_group,
                            int32_t n_groups,
                            vm_engine** out);
-void vm_engine_destroy(vm_engine* engine);
+VM_API void vm_engine_destroy(vm_engine* engine);
 
 /* Uploads one mesh (one camera height) once, as the OpenCL engine caches rays per mesh
  * (cpp/visualmesh/engine/opencl/engine.hpp:603-625). rays is n_nodes x 3, neighbours n_nodes x n_neighbours
  * (visualmesh::Node, cpp/visualmesh/node.hpp:40-46); neighbour value n_nodes = no such node. n_neighbours in {4,6,8}. */
-vm_status vm_mesh_upload(vm_engine* engine,
+VM_API vm_status vm_mesh_upload(vm_engine* engine,
                          const float* rays,
                          const int32_t* neighbours,
                          int32_t n_nodes,
@@ -127,30 +133,30 @@ vm_status vm_mesh_upload(vm_engine* engine,
 /* Adds the mesh's binary space partition (cpp/visualmesh/mesh.hpp:66-83): per element its node range [start,end),
  * its two children (-1,-1 for a leaf) and its bounding cone (axis xyz, cos, sin). With it frames may pass
  * ranges == NULL and Mesh::lookup (cpp/visualmesh/mesh.hpp:499-595) runs on the device. */
-vm_status vm_mesh_set_bsp(vm_engine* engine,
+VM_API vm_status vm_mesh_set_bsp(vm_engine* engine,
                           vm_mesh* mesh,
                           int32_t n_elements,
                           const int32_t* element_ranges,
                           const int32_t* element_children,
                           const float* element_cones);
 /* Counterpart of clear_cache() (cpp/visualmesh/engine/opencl/engine.hpp:559-572) for one mesh. */
-void vm_mesh_release(vm_engine* engine, vm_mesh* mesh);
+VM_API void vm_mesh_release(vm_engine* engine, vm_mesh* mesh);
 
 /* The hot path over a batch of independent frames in one set of kernel launches.
  * All frames of a batch must use meshes with the same n_neighbours. */
-vm_status vm_run_batch(vm_engine* engine, const vm_frame* frames, int32_t n_frames, uint32_t flags, vm_batch_result* out);
+VM_API vm_status vm_run_batch(vm_engine* engine, const vm_frame* frames, int32_t n_frames, uint32_t flags, vm_batch_result* out);
 
 /* Single-frame forms of the two reference calls (batches of one).
  * vm_project  = operator()(mesh, Hoc, lens)                cpp/visualmesh/engine/cpu/engine.hpp:85-147
  * vm_classify = operator()(mesh, Hoc, lens, image, format) cpp/visualmesh/engine/cpu/engine.hpp:181-273 */
-vm_status vm_project(vm_engine* engine,
+VM_API vm_status vm_project(vm_engine* engine,
                      const vm_mesh* mesh,
                      const int32_t* ranges,
                      int32_t n_ranges,
                      const float Hoc[16],
                      const vm_lens* lens,
                      vm_batch_result* out);
-vm_status vm_classify(vm_engine* engine,
+VM_API vm_status vm_classify(vm_engine* engine,
                       const vm_mesh* mesh,
                       const int32_t* ranges,
                       int32_t n_ranges,
@@ -165,7 +171,7 @@ vm_status vm_classify(vm_engine* engine,
  * vm_sample: cpu::interpolate (cpp/visualmesh/engine/cpu/pixel.hpp:116-144) at n pixel coordinates -> n x 4 floats.
  * vm_network: the gather/dense/activation loop (cpp/visualmesh/engine/cpu/engine.hpp:213-265) over n_rows rows
  *             (last row = off-screen row) of 4 input floats with an n_rows x n_neighbours neighbourhood. */
-vm_status vm_sample(vm_engine* engine,
+VM_API vm_status vm_sample(vm_engine* engine,
                     const float* pixel_coordinates,
                     int32_t n,
                     const void* image,
@@ -173,7 +179,7 @@ vm_status vm_sample(vm_engine* engine,
                     int32_t height,
                     uint32_t format,
                     float* out);
-vm_status vm_network(vm_engine* engine,
+VM_API vm_status vm_network(vm_engine* engine,
                      const float* input,
                      const int32_t* neighbourhood,
                      int32_t n_rows,
@@ -182,17 +188,17 @@ vm_status vm_network(vm_engine* engine,
 
 /* Kernel time of the last vm_run_batch called with VM_TIME_STAGES, one entry per launched kernel in launch order.
  * Returns the number of stages through *n; names[i] points at a static string. */
-vm_status vm_stage_times(vm_engine* engine, const char** names, float* milliseconds, int32_t capacity, int32_t* n);
+VM_API vm_status vm_stage_times(vm_engine* engine, const char** names, float* milliseconds, int32_t capacity, int32_t* n);
 
 /* Number of kernels launched by this engine since creation. */
-int64_t vm_launch_count(const vm_engine* engine);
+VM_API int64_t vm_launch_count(const vm_engine* engine);
 
 /* Pinned host memory for callers that want zero-staging copies of their frames. */
-vm_status vm_host_alloc(void** ptr, size_t bytes);
-void vm_host_free(void* ptr);
+VM_API vm_status vm_host_alloc(void** ptr, size_t bytes);
+VM_API void vm_host_free(void* ptr);
 
 /* Message of the last failing call on this thread. */
-const char* vm_last_error(void);
+VM_API const char* vm_last_error(void);
 
 /* ------------------------------------------------------------------------------------------------------------------
  * Host-side mesh tables for callers that are not C++ and cannot instantiate the reference's templates:
@@ -203,7 +209,7 @@ typedef struct vm_hostmesh vm_hostmesh;
 
 /* model: "RING4" "RING6" "RING8" "XYGRID4" "XYGRID6" "XYGRID8"; shape: "SPHERE" (a = radius), "CIRCLE" (a = radius),
  * "CYLINDER" (a = radius, b = height). */
-vm_status vm_hostmesh_create(const char* model,
+VM_API vm_status vm_hostmesh_create(const char* model,
                              const char* shape,
                              float shape_a,
                              float shape_b,
@@ -211,16 +217,16 @@ vm_status vm_hostmesh_create(const char* model,
                              float k,
                              float max_distance,
                              vm_hostmesh** out);
-void vm_hostmesh_destroy(vm_hostmesh* mesh);
-int32_t vm_hostmesh_n_nodes(const vm_hostmesh* mesh);
-int32_t vm_hostmesh_n_neighbours(const vm_hostmesh* mesh);
-int32_t vm_hostmesh_n_bsp(const vm_hostmesh* mesh);
+VM_API void vm_hostmesh_destroy(vm_hostmesh* mesh);
+VM_API int32_t vm_hostmesh_n_nodes(const vm_hostmesh* mesh);
+VM_API int32_t vm_hostmesh_n_neighbours(const vm_hostmesh* mesh);
+VM_API int32_t vm_hostmesh_n_bsp(const vm_hostmesh* mesh);
 /* rays: n_nodes x 3, neighbours: n_nodes x n_neighbours */
-vm_status vm_hostmesh_nodes(const vm_hostmesh* mesh, float* rays, int32_t* neighbours);
+VM_API vm_status vm_hostmesh_nodes(const vm_hostmesh* mesh, float* rays, int32_t* neighbours);
 /* ranges: n_bsp x 2, children: n_bsp x 2, cones: n_bsp x 5 */
-vm_status vm_hostmesh_bsp(const vm_hostmesh* mesh, int32_t* ranges, int32_t* children, float* cones);
+VM_API vm_status vm_hostmesh_bsp(const vm_hostmesh* mesh, int32_t* ranges, int32_t* children, float* cones);
 /* Mesh::lookup on the host; writes up to capacity pairs, returns the number of ranges through *n_ranges. */
-vm_status vm_hostmesh_lookup(const vm_hostmesh* mesh,
+VM_API vm_status vm_hostmesh_lookup(const vm_hostmesh* mesh,
                              const float Hoc[16],
                              const vm_lens* lens,
                              int32_t* ranges,

@@ -1,0 +1,242 @@
+"""Parity of the CUDA engine with the reference CPU engine, through the C ABI. Needs a GPU (-m gpu).
+
+Layers of the check, so that a last-bit difference of a transcendental cannot hide a real defect:
+  1. projection alone: on-screen set, neighbourhood, pixel coordinates;
+  2. sampler and network alone, fed with the REFERENCE's pixel coordinates and neighbourhood: must match to 1e-4
+     (in practice ~1e-6; the only difference is fused multiply-add and the device's expf);
+  3. the whole call, host ranges and device lookup, Python front end and the C++ drop-in header.
+On uniform-noise images one ulp of a pixel coordinate already moves a classification by more than 1e-4 through an
+8-layer network, and the host libm's acosf/sinf/tanf are not correctly rounded while the device evaluates them in
+double and rounds once; the end-to-end checks therefore bound the fraction of entries over tolerance instead of
+demanding zero, and print what they saw.
+"""
+import numpy as np
+import pytest
+
+import golden_io as G
+import oracle as O
+import parity as P
+import refharness as R
+from visualmesh_b200 import workloads as W
+from visualmesh_b200.engine import Engine, FrameInput, Mesh, VisualMeshError
+
+pytestmark = pytest.mark.gpu
+
+
+def _mesh_from_case(case):
+    return Mesh.from_arrays(case.rays, case.nbrs, case.bsp)
+
+
+@pytest.fixture(scope="module")
+def cases():
+    return {name: G.Case(name) for name in G.CASES}
+
+
+# ---- 1 + 3: golden fixtures, whole call -----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", G.CASES)
+@pytest.mark.parametrize("lookup", ["host_ranges", "device_lookup"])
+def test_golden_whole_call(cases, name, lookup):
+    case = cases[name]
+    engine = Engine(case.network)
+    mesh = _mesh_from_case(case)
+    for f, fr in enumerate(case.frames):
+        ranges = fr["ranges"] if lookup == "host_ranges" else None
+        out = engine.run_batch([FrameInput(mesh, fr["Hoc"], case.lens, fr["image"], case.format, ranges)]).frame(0)
+        rep = P.compare(out, fr, case.lens.dimensions)
+        print(f"{name}[{f}] {lookup}: {rep}")
+        assert rep.projection_ok, str(rep)
+        assert rep.n_out == rep.n_ref or rep.border_nodes
+        assert rep.max_cls < 5e-3, str(rep)
+        assert rep.cls_over_tol <= max(2, rep.cls_entries // 200), str(rep)
+    engine.close()
+
+
+@pytest.mark.parametrize("name", G.CASES)
+def test_golden_projection_only(cases, name):
+    case = cases[name]
+    engine = Engine()
+    mesh = _mesh_from_case(case)
+    for f, fr in enumerate(case.frames):
+        out = engine(mesh, fr["Hoc"], case.lens, ranges=fr["ranges"])
+        assert not hasattr(out, "classifications") or out.classifications is None
+        rep = P.compare(out, {k: fr[k] for k in ("pixel_coordinates", "neighbourhood", "global_indices")},
+                        case.lens.dimensions)
+        assert rep.projection_ok, str(rep)
+        if len(fr["global_indices"]) == 0:
+            assert out.global_indices.size == 0
+    engine.close()
+
+
+# ---- 2: stages alone, identical inputs ------------------------------------------------------------------------------
+
+def test_sampler_bit_exact_for_every_fourcc():
+    z, _ = G.units()
+    Wd, Ht = [int(v) for v in z["sample_dims"]]
+    engine = Engine()
+    for code in ["RGGB", "GRBG", "GBRG", "BGGR", "BGR3", "BGR8", "BGRA", "RGB3", "RGB8", "RGBA", "GRAY", "GREY",
+                 "Y8  "]:
+        out = engine.sample(z["sample_px"], z[f"sample_image_{code.strip()}"], Wd, Ht, W.fourcc(code))
+        assert np.array_equal(G.bits(out), G.bits(z[f"sample_out_{code.strip()}"])), code
+    engine.close()
+
+
+@pytest.mark.parametrize("name", G.CASES)
+def test_network_on_reference_inputs(cases, name):
+    case = cases[name]
+    engine = Engine(case.network)
+    for f, fr in enumerate(case.frames):
+        n = len(fr["global_indices"])
+        if n == 0:
+            continue
+        sampled = engine.sample(fr["pixel_coordinates"], fr["image"], *case.lens.dimensions, case.format)
+        want = O.interpolate(fr["pixel_coordinates"], fr["image"], *case.lens.dimensions, case.format)
+        assert np.array_equal(G.bits(sampled), G.bits(want)), f"{name}[{f}] sampler"
+        inputs = np.concatenate([sampled, -np.ones((1, 4), np.float32)])
+        out = engine.network(inputs, fr["neighbourhood"])
+        d = np.abs(out.astype(np.float64) - fr["classifications"].astype(np.float64)).max()
+        print(f"{name}[{f}] network on reference inputs: max |d| = {d:.3g}")
+        assert d <= P.TOL_CLS
+    engine.close()
+
+
+# ---- batches ---------------------------------------------------------------------------------------------------------
+
+def test_batch_equals_single_frames_bit_for_bit(cases):
+    case = cases["ring6_equisolid_rgba"]
+    engine = Engine(case.network)
+    mesh = _mesh_from_case(case)
+    frames = []
+    for rep in range(3):  # 9 frames, mixing host ranges and device lookup
+        for f, fr in enumerate(case.frames):
+            frames.append(FrameInput(mesh, fr["Hoc"], case.lens, fr["image"], case.format,
+                                     fr["ranges"] if (rep + f) % 2 == 0 else None))
+    singles = [engine.run_batch([fr]).frame(0) for fr in frames]
+    import os
+    os.environ["VMCUDA_CHUNK_FRAMES"] = "2"  # several chunks rotating over the lanes
+    engine2 = Engine(case.network)
+    os.environ.pop("VMCUDA_CHUNK_FRAMES")
+    mesh2 = _mesh_from_case(case)
+    frames2 = [FrameInput(mesh2, fr.Hoc, fr.lens, fr.image, fr.format, fr.ranges) for fr in frames]
+    for eng, frs in ((engine, frames), (engine2, frames2)):
+        batch = eng.run_batch(frs)
+        assert batch.n_frames == len(frames)
+        for f, single in enumerate(singles):
+            got = batch.frame(f)
+            for key in ("pixel_coordinates", "global_indices", "neighbourhood", "classifications"):
+                assert np.array_equal(G.bits(getattr(got, key)), G.bits(getattr(single, key))), f"frame {f} {key}"
+    engine.close()
+    engine2.close()
+
+
+def test_empty_frames_and_empty_ranges(cases):
+    case = cases["ring4_rectilinear_grey"]
+    engine = Engine(case.network)
+    mesh = _mesh_from_case(case)
+    fr = case.frames[1]  # camera looks up: nothing on screen
+    assert len(fr["global_indices"]) == 0
+    for ranges in (fr["ranges"], None):
+        out = engine.run_batch([FrameInput(mesh, fr["Hoc"], case.lens, fr["image"], case.format, ranges)]).frame(0)
+        assert out.global_indices.size == 0 and out.classifications.size == 0
+    # an empty frame between two full ones does not disturb them
+    full = case.frames[0]
+    batch = engine.run_batch([FrameInput(mesh, full["Hoc"], case.lens, full["image"], case.format, full["ranges"]),
+                              FrameInput(mesh, fr["Hoc"], case.lens, fr["image"], case.format, fr["ranges"]),
+                              FrameInput(mesh, full["Hoc"], case.lens, full["image"], case.format, None)])
+    a, b = batch.frame(0), batch.frame(2)
+    assert batch.frame(1).global_indices.size == 0
+    assert np.array_equal(a.global_indices, full["global_indices"])
+    assert np.array_equal(G.bits(a.classifications), G.bits(b.classifications))
+    engine.close()
+
+
+def test_errors_match_the_reference_conditions(cases):
+    case = cases["ring6_equisolid_rgba"]
+    engine = Engine(case.network)
+    mesh = _mesh_from_case(case)
+    fr = case.frames[0]
+    with pytest.raises(VisualMeshError) as e:
+        engine(mesh, fr["Hoc"], case.lens, fr["image"], W.fourcc("NV12"), ranges=fr["ranges"])
+    assert e.value.status == 2 and "Unsupported image format" in str(e.value)
+    bad = W.Lens(case.lens.dimensions, 9, case.lens.focal_length)
+    with pytest.raises(VisualMeshError) as e:
+        engine(mesh, fr["Hoc"], bad, fr["image"], case.format, ranges=fr["ranges"])
+    assert e.value.status == 3
+    no_bsp = Mesh.from_arrays(case.rays, case.nbrs, None)
+    with pytest.raises(VisualMeshError) as e:
+        engine.run_batch([FrameInput(no_bsp, fr["Hoc"], case.lens, fr["image"], case.format, None)])
+    assert e.value.status == 8
+    # the engine is still usable after a failed call
+    out = engine(mesh, fr["Hoc"], case.lens, fr["image"], case.format, ranges=fr["ranges"])
+    assert np.array_equal(out.global_indices, fr["global_indices"])
+    engine.close()
+
+
+# ---- benchmark configurations against the compiled reference -------------------------------------------------------
+
+needs_ref = pytest.mark.skipif(not R.available(), reason="compiled reference (oracle/_ref/libvmref.so) not present")
+
+
+def _check_config(cfg, n_frames, via_cpp):
+    wl = W.config(cfg, n_frames=n_frames)
+    ref_meshes, own_meshes = {}, {}
+    engine = Engine(wl.network)
+    frames_ok = 0
+    for f, fr in enumerate(wl.frames):
+        ref_mesh = ref_meshes.setdefault(fr.mesh.key(), R.RefMesh(fr.mesh))
+        image = fr.image()
+        ref = ref_mesh.classify(wl.network, fr.Hoc, fr.lens, image, fr.format)
+        if via_cpp:
+            out = ref_mesh.classify(wl.network, fr.Hoc, fr.lens, image, fr.format, cuda=True)
+        else:
+            if fr.mesh.key() not in own_meshes:
+                own_meshes[fr.mesh.key()] = Mesh.from_spec(fr.mesh)
+            out = engine.run_batch([FrameInput(own_meshes[fr.mesh.key()], fr.Hoc, fr.lens, image, fr.format,
+                                               None)]).frame(0)
+        rep = P.compare(out, ref, fr.lens.dimensions)
+        print(f"cfg{cfg}[{f}] {'c++ drop-in' if via_cpp else 'python/C-ABI'}: {rep}")
+        assert rep.projection_ok, str(rep)
+        assert rep.n_ref > 0
+        assert rep.max_cls < 2e-2, str(rep)
+        assert rep.cls_over_tol <= max(2, rep.cls_entries // 200), str(rep)
+        frames_ok += rep.ok
+    engine.close()
+    return frames_ok
+
+
+@needs_ref
+@pytest.mark.parametrize("cfg,n_frames", [(0, 1), (1, 3), (2, 3), (4, 4)])
+def test_benchmark_config_vs_compiled_reference(cfg, n_frames):
+    _check_config(cfg, n_frames, via_cpp=False)
+
+
+def _harness_has_drop_in():
+    try:
+        return R.available() and hasattr(R.lib(), "vmref_cuda_classify")
+    except OSError:
+        return False
+
+
+@needs_ref
+@pytest.mark.skipif(not _harness_has_drop_in(), reason="harness built without the CUDA drop-in")
+@pytest.mark.parametrize("cfg,n_frames", [(0, 1), (2, 2)])
+def test_cpp_drop_in_engine_vs_cpu_engine_on_the_same_mesh_object(cfg, n_frames):
+    _check_config(cfg, n_frames, via_cpp=True)
+
+
+@needs_ref
+def test_config3_dense_mesh_projection_and_two_layers():
+    """Config 3's mesh (1.7M nodes, 0.93M on screen) with a cut-down network so the CPU reference finishes quickly."""
+    wl = W.config(3, n_frames=1)
+    fr = wl.frames[0]
+    net = wl.network[:1] + [[W.Layer(wl.network[-1][0].weights, wl.network[-1][0].biases, W.SOFTMAX)]]
+    ref_mesh = R.RefMesh(fr.mesh)
+    image = fr.image()
+    ref = ref_mesh.classify(net, fr.Hoc, fr.lens, image, fr.format)
+    engine = Engine(net)
+    out = engine.run_batch([FrameInput(Mesh.from_spec(fr.mesh), fr.Hoc, fr.lens, image, fr.format, None)]).frame(0)
+    rep = P.compare(out, ref, fr.lens.dimensions)
+    print(f"cfg3 (2 layers): {rep}")
+    assert rep.projection_ok and rep.n_ref > 900000, str(rep)
+    assert rep.cls_over_tol <= rep.cls_entries // 200, str(rep)
+    engine.close()

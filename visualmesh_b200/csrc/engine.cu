@@ -1,0 +1,983 @@
+// Host side of the engine and its C ABI (include/vmcuda.h).
+//
+// One engine instance owns its streams, its grow-only device scratch and its pinned result buffers; like the
+// reference engines it is not thread-safe - use one instance per host thread. A batch is cut into chunks of frames;
+// chunks rotate over a few lanes (stream + scratch) so that the host-to-device copy of one chunk's images, the
+// kernels of another and the device-to-host copy of a third overlap.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/vmcuda.h"
+#include "host_math.hpp"
+#include "kernels.cuh"
+
+namespace vm {
+
+static thread_local std::string g_error;
+
+static vm_status fail(vm_status s, const std::string& msg) {
+    g_error = msg;
+    return s;
+}
+
+struct CudaFailure {
+    cudaError_t code;
+    const char* what;
+};
+
+#define VM_CUDA(expr)                                        \
+    do {                                                     \
+        cudaError_t vm_e_ = (expr);                          \
+        if (vm_e_ != cudaSuccess) throw CudaFailure{vm_e_, #expr}; \
+    } while (0)
+
+// Grow-only device and pinned-host arrays (the reference's OpenCL engine keeps the same kind of caches,
+// cpp/visualmesh/engine/opencl/engine.hpp:740-835).
+template <typename T>
+struct DeviceArray {
+    T* p       = nullptr;
+    size_t cap = 0;
+    void ensure(size_t n) {
+        if (n <= cap) return;
+        if (p != nullptr) VM_CUDA(cudaFree(p));
+        p   = nullptr;
+        cap = 0;
+        const size_t want = n + n / 8 + 64;
+        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&p), want * sizeof(T)));
+        cap = want;
+    }
+    void release() {
+        if (p != nullptr) cudaFree(p);
+        p   = nullptr;
+        cap = 0;
+    }
+};
+
+template <typename T>
+struct PinnedArray {
+    T* p       = nullptr;
+    size_t cap = 0;
+    void ensure(size_t n) {
+        if (n <= cap) return;
+        if (p != nullptr) VM_CUDA(cudaFreeHost(p));
+        p   = nullptr;
+        cap = 0;
+        const size_t want = n + n / 8 + 64;
+        VM_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&p), want * sizeof(T), cudaHostAllocDefault));
+        cap = want;
+    }
+    void release() {
+        if (p != nullptr) cudaFreeHost(p);
+        p   = nullptr;
+        cap = 0;
+    }
+};
+
+struct DenseLayer {
+    float* d_weights = nullptr;  // [n_slots * cin][coutp] then [coutp] biases
+    int cin = 0, cout = 0, coutp = 0, n_slots = 1, activation = 0;
+};
+
+constexpr int MAX_LANES = 3;
+
+struct Lane {
+    cudaStream_t stream   = nullptr;
+    cudaEvent_t ev_staged = nullptr;   // host staging of this lane has been consumed
+    cudaEvent_t ev_scan   = nullptr;   // this chunk's offsets are on the device
+    cudaEvent_t ev_offsets = nullptr;  // ... and on the host
+    cudaEvent_t ev_done   = nullptr;   // everything of this chunk, copies included, has finished
+    bool busy             = false;
+    int f0 = 0, f1 = 0;
+    PinnedArray<FrameParams> h_frames;
+    DeviceArray<FrameParams> d_frames;
+    PinnedArray<int32_t> h_ranges;  // int2 ranges then range starts
+    DeviceArray<int32_t> d_ranges;
+    DeviceArray<uint8_t> d_state;
+    DeviceArray<float2> d_cand_px;
+    DeviceArray<int32_t> d_cand_node;
+    DeviceArray<int32_t> d_block_counts;
+    DeviceArray<int32_t> d_node_rank;
+    DeviceArray<float> d_feat[2];
+    DeviceArray<uint8_t> d_images;
+};
+
+struct StageTimer {
+    const char* name;
+    cudaEvent_t start, stop;
+};
+
+}  // namespace vm
+
+struct vm_mesh {
+    int32_t n_nodes = 0, n_neighbours = 0, n_bsp = 0;
+    float4* d_rays        = nullptr;
+    int32_t* d_neighbours = nullptr;
+    float4* d_cones_a     = nullptr;
+    float* d_cones_s      = nullptr;
+    int4* d_topology      = nullptr;
+};
+
+struct vm_engine {
+    int device = 0;
+    std::vector<vm::DenseLayer> layers;
+    int max_width = 4;
+    int n_classes = 0;
+    vm::Lane lanes[vm::MAX_LANES];
+    int n_lanes = vm::MAX_LANES;
+    int64_t chunk_candidates = 2 << 20;
+    int chunk_frames         = 16;
+    // batch-wide results
+    vm::DeviceArray<int32_t> d_offsets;
+    vm::PinnedArray<int32_t> h_offsets;
+    vm::DeviceArray<float2> d_px;
+    vm::DeviceArray<int32_t> d_gi;
+    vm::DeviceArray<int32_t> d_nb;
+    vm::DeviceArray<float> d_cls;
+    vm::PinnedArray<float2> h_px;
+    vm::PinnedArray<int32_t> h_gi;
+    vm::PinnedArray<int32_t> h_nb;
+    vm::PinnedArray<float> h_cls;
+    int32_t* d_abort = nullptr;
+    int32_t* h_abort = nullptr;
+    std::vector<vm_mesh*> meshes;
+    // stage timing
+    std::vector<vm::StageTimer> timers;
+    std::vector<cudaEvent_t> event_pool;
+    size_t events_used = 0;
+    bool timing        = false;
+    std::vector<std::pair<const char*, float>> stage_ms;
+    int64_t launches = 0;
+};
+
+namespace vm {
+
+static void begin_stage(vm_engine* e, cudaStream_t s, const char* name) {
+    ++e->launches;
+    if (!e->timing) return;
+    while (e->event_pool.size() < e->events_used + 2) {
+        cudaEvent_t ev;
+        VM_CUDA(cudaEventCreate(&ev));
+        e->event_pool.push_back(ev);
+    }
+    StageTimer t{name, e->event_pool[e->events_used], e->event_pool[e->events_used + 1]};
+    e->events_used += 2;
+    VM_CUDA(cudaEventRecord(t.start, s));
+    e->timers.push_back(t);
+}
+static void end_stage(vm_engine* e, cudaStream_t s) {
+    if (!e->timing) return;
+    VM_CUDA(cudaEventRecord(e->timers.back().stop, s));
+}
+
+// ---- graph convolution dispatch ----------------------------------------------------------------------------------
+
+template <int CIN, int COUT, int R>
+static void launch_conv_t(const ConvArgs& a, dim3 grid_rows, int max_rows, cudaStream_t s) {
+    constexpr int COUTP = (COUT + 3) & ~3;
+    const size_t smem   = (static_cast<size_t>(a.n_slots) * CIN * COUTP + COUTP) * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        VM_CUDA(cudaFuncSetAttribute(k_graph_conv<CIN, COUT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        configured = true;
+    }
+    dim3 grid((max_rows + CONV_THREADS * R - 1) / (CONV_THREADS * R), grid_rows.y);
+    k_graph_conv<CIN, COUT, R><<<grid, CONV_THREADS, smem, s>>>(a);
+}
+
+// Shapes with a specialised kernel; anything else takes the generic one.
+static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, int max_rows, cudaStream_t s) {
+    const size_t smem = (static_cast<size_t>(a.n_slots) * L.cin * L.coutp + L.coutp) * sizeof(float);
+    if (smem > 96 * 1024) return false;
+#define VM_CONV(CI, CO, RR)                                   \
+    if (L.cin == CI && L.cout == CO) {                        \
+        launch_conv_t<CI, CO, RR>(a, grid, max_rows, s);      \
+        return true;                                          \
+    }
+    VM_CONV(4, 2, 4) VM_CONV(4, 3, 4) VM_CONV(4, 4, 4) VM_CONV(4, 8, 4) VM_CONV(4, 12, 4) VM_CONV(4, 16, 4) VM_CONV(4, 32, 2)
+    VM_CONV(8, 2, 4) VM_CONV(8, 3, 4) VM_CONV(8, 4, 4) VM_CONV(8, 5, 4) VM_CONV(8, 8, 4) VM_CONV(8, 12, 4) VM_CONV(8, 16, 4)
+    VM_CONV(12, 2, 4) VM_CONV(12, 3, 4) VM_CONV(12, 4, 4) VM_CONV(12, 8, 4) VM_CONV(12, 12, 4) VM_CONV(12, 16, 4)
+    VM_CONV(16, 2, 4) VM_CONV(16, 3, 4) VM_CONV(16, 4, 4) VM_CONV(16, 5, 4) VM_CONV(16, 8, 4) VM_CONV(16, 12, 4) VM_CONV(16, 16, 4)
+    VM_CONV(16, 32, 2)
+    VM_CONV(32, 2, 4) VM_CONV(32, 3, 4) VM_CONV(32, 4, 4) VM_CONV(32, 8, 4) VM_CONV(32, 16, 4) VM_CONV(32, 32, 2)
+#undef VM_CONV
+    return false;
+}
+
+static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_frames, int max_rows, cudaStream_t s) {
+    a.weights     = L.d_weights;
+    a.biases      = L.d_weights + static_cast<size_t>(L.n_slots) * L.cin * L.coutp;
+    a.n_slots     = L.n_slots;
+    a.activation  = L.activation;
+    dim3 grid(1, n_frames);
+    begin_stage(e, s, "graph_conv");
+    if (!launch_conv_fast(L, a, grid, max_rows, s)) {
+        dim3 g((max_rows + CONV_THREADS - 1) / CONV_THREADS, n_frames);
+        k_graph_conv_generic<<<g, CONV_THREADS, 0, s>>>(a, L.cin, L.cout, L.coutp);
+    }
+    VM_CUDA(cudaGetLastError());
+    end_stage(e, s);
+}
+
+// Runs all layers over a chunk whose input features are in feat[0]; the last layer writes out_final.
+static void run_network(vm_engine* e,
+                        Lane& lane,
+                        const int32_t* d_offsets,
+                        const int32_t* d_nb,
+                        int n_neighbours,
+                        int f0,
+                        int n_frames,
+                        int max_rows,
+                        float* out_final,
+                        bool final_global) {
+    int cur = 0;
+    for (size_t l = 0; l < e->layers.size(); ++l) {
+        const bool last = l + 1 == e->layers.size();
+        ConvArgs a{};
+        a.in           = lane.d_feat[cur].p;
+        a.out          = last ? out_final : lane.d_feat[cur ^ 1].p;
+        a.nb           = d_nb;
+        a.offsets      = d_offsets;
+        a.n_neighbours = n_neighbours;
+        a.f0           = f0;
+        a.out_global   = (last && final_global) ? 1 : 0;
+        launch_conv(e, e->layers[l], a, n_frames, max_rows, lane.stream);
+        cur ^= 1;
+    }
+}
+
+// ---- per-frame constants -----------------------------------------------------------------------------------------
+
+static bool fill_frame_params(const vm_frame& fr, FrameParams& p) {
+    const float* H = fr.Hoc;
+    // Rco = block<3,3>(transpose(Hoc)), cpp/visualmesh/engine/cpu/engine.hpp:95
+    for (int i = 0; i < 3; ++i)
+        for (int j = 0; j < 3; ++j) p.Rco[i * 3 + j] = H[j * 4 + i];
+    p.focal_length = fr.lens.focal_length;
+    p.centre[0]    = fr.lens.centre[0];
+    p.centre[1]    = fr.lens.centre[1];
+    p.half_dims[0] = float(fr.lens.dimensions[0]) * 0.5f;
+    p.half_dims[1] = float(fr.lens.dimensions[1]) * 0.5f;
+    host::inverse_coefficients(fr.lens.k, p.ik);
+    p.dims[0]    = fr.lens.dimensions[0];
+    p.dims[1]    = fr.lens.dimensions[1];
+    p.projection = fr.lens.projection;
+    p.format     = fr.format;
+    // cpp/visualmesh/mesh.hpp:503-504
+    p.cos_fov = std::cos(fr.lens.fov * 0.5f);
+    p.sin_fov = std::sin(fr.lens.fov * 0.5f);
+    if (fr.ranges == nullptr) {
+        std::array<host::Cone, 4> edges;
+        if (!host::screen_edges(H, fr.lens, edges)) return false;
+        for (int i = 0; i < 4; ++i) {
+            p.edges[i][0] = edges[i].axis[0];
+            p.edges[i][1] = edges[i].axis[1];
+            p.edges[i][2] = edges[i].axis[2];
+            p.edges[i][3] = edges[i].cos_t;
+            p.edges[i][4] = edges[i].sin_t;
+        }
+    }
+    const vm_mesh* m = fr.mesh;
+    p.rays           = m->d_rays;
+    p.neighbours     = m->d_neighbours;
+    p.bsp_cones_a    = m->d_cones_a;
+    p.bsp_cones_s    = m->d_cones_s;
+    p.bsp_topology   = m->d_topology;
+    p.n_nodes        = m->n_nodes;
+    p.n_bsp          = m->n_bsp;
+    return true;
+}
+
+static size_t image_bytes(const vm_frame& fr) {
+    const int cls = format_class(fr.format);
+    return static_cast<size_t>(fr.lens.dimensions[0]) * fr.lens.dimensions[1] * format_bytes_per_pixel(cls);
+}
+
+static int64_t frame_candidates(const vm_frame& fr) {
+    if (fr.ranges == nullptr) return fr.mesh->n_nodes;
+    int64_t n = 0;
+    for (int r = 0; r < fr.n_ranges; ++r) n += std::max(0, fr.ranges[2 * r + 1] - fr.ranges[2 * r]);
+    return n;
+}
+
+// ---- one chunk: enqueue everything up to the last kernel -----------------------------------------------------
+
+static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* frames, int f0, int f1, bool classify) {
+    const int nf = f1 - f0;
+    cudaStream_t s = lane.stream;
+    lane.f0 = f0;
+    lane.f1 = f1;
+
+    // host staging: frame constants and the concatenated ranges
+    lane.h_frames.ensure(nf);
+    lane.d_frames.ensure(nf);
+    size_t n_ranges_total = 0;
+    for (int f = f0; f < f1; ++f) n_ranges_total += frames[f].ranges != nullptr ? frames[f].n_ranges : 0;
+    lane.h_ranges.ensure(3 * n_ranges_total + 4);
+    lane.d_ranges.ensure(3 * n_ranges_total + 4);
+
+    int64_t cand_total = 0, node_total = 0, bsp_total = 0, image_total = 0;
+    int32_t max_cand = 0;
+    bool any_device_lookup = false, any_host_ranges = false;
+    size_t range_cursor = 0;
+    for (int f = f0; f < f1; ++f) {
+        const vm_frame& fr = frames[f];
+        FrameParams& p     = lane.h_frames.p[f - f0];
+        std::memset(&p, 0, sizeof(p));
+        fill_frame_params(fr, p);
+        const int64_t nc = frame_candidates(fr);
+        p.n_candidates   = static_cast<int32_t>(nc);
+        p.cand_off       = static_cast<int32_t>(cand_total);
+        p.node_off       = static_cast<int32_t>(node_total);
+        p.bsp_off        = static_cast<int32_t>(bsp_total);
+        if (fr.ranges != nullptr) {
+            any_host_ranges = true;
+            // device layout: [int2 ranges of all frames][starts of all frames]; pointers are patched below
+            p.n_ranges = fr.n_ranges;
+        }
+        else {
+            any_device_lookup = true;
+            bsp_total += fr.mesh->n_bsp;
+        }
+        cand_total += nc;
+        node_total += fr.mesh->n_nodes;
+        max_cand = std::max<int32_t>(max_cand, static_cast<int32_t>(nc));
+        if (classify && !fr.image_on_device) image_total += (image_bytes(fr) + 255) & ~size_t(255);
+    }
+    // ranges and their exclusive prefix sums
+    {
+        int32_t* pairs  = lane.h_ranges.p;
+        int32_t* starts = lane.h_ranges.p + 2 * n_ranges_total;
+        for (int f = f0; f < f1; ++f) {
+            const vm_frame& fr = frames[f];
+            if (fr.ranges == nullptr) continue;
+            FrameParams& p = lane.h_frames.p[f - f0];
+            p.ranges       = reinterpret_cast<const int2*>(lane.d_ranges.p + 2 * range_cursor);
+            p.range_starts = lane.d_ranges.p + 2 * n_ranges_total + range_cursor;
+            int32_t run    = 0;
+            for (int r = 0; r < fr.n_ranges; ++r) {
+                pairs[2 * (range_cursor + r) + 0] = fr.ranges[2 * r];
+                pairs[2 * (range_cursor + r) + 1] = fr.ranges[2 * r + 1];
+                starts[range_cursor + r]          = run;
+                run += std::max(0, fr.ranges[2 * r + 1] - fr.ranges[2 * r]);
+            }
+            if (fr.n_ranges == 0) {
+                // keep the "host ranges" marker non-null for an empty frame
+                p.ranges       = reinterpret_cast<const int2*>(lane.d_ranges.p);
+                p.range_starts = lane.d_ranges.p;
+            }
+            range_cursor += fr.n_ranges;
+        }
+    }
+
+    lane.d_cand_px.ensure(cand_total + 1);
+    lane.d_cand_node.ensure(cand_total + 1);
+    lane.d_node_rank.ensure(node_total + 1);
+    if (any_device_lookup) lane.d_state.ensure(bsp_total + 1);
+    const int blocks_per_frame = std::max(1, (max_cand + SELECT_THREADS - 1) / SELECT_THREADS);
+    const int n_blocks         = blocks_per_frame * nf;
+    lane.d_block_counts.ensure(n_blocks + 1);
+    const int64_t rows_cap = cand_total + nf;
+    if (classify) {
+        lane.d_feat[0].ensure(static_cast<size_t>(rows_cap) * e->max_width);
+        lane.d_feat[1].ensure(static_cast<size_t>(rows_cap) * e->max_width);
+        lane.d_images.ensure(image_total + 256);
+    }
+
+    // images: host frames go through the lane's device buffer, device frames are read in place
+    if (classify) {
+        size_t cursor = 0;
+        for (int f = f0; f < f1; ++f) {
+            const vm_frame& fr = frames[f];
+            FrameParams& p     = lane.h_frames.p[f - f0];
+            if (fr.image_on_device) { p.image = static_cast<const uint8_t*>(fr.image); }
+            else {
+                const size_t bytes = image_bytes(fr);
+                VM_CUDA(cudaMemcpyAsync(lane.d_images.p + cursor, fr.image, bytes, cudaMemcpyHostToDevice, s));
+                p.image = lane.d_images.p + cursor;
+                cursor += (bytes + 255) & ~size_t(255);
+            }
+        }
+    }
+    VM_CUDA(cudaMemcpyAsync(lane.d_frames.p, lane.h_frames.p, sizeof(FrameParams) * nf, cudaMemcpyHostToDevice, s));
+    if (n_ranges_total > 0) {
+        VM_CUDA(cudaMemcpyAsync(lane.d_ranges.p, lane.h_ranges.p, sizeof(int32_t) * 3 * n_ranges_total, cudaMemcpyHostToDevice, s));
+    }
+    VM_CUDA(cudaEventRecord(lane.ev_staged, s));
+
+    if (any_host_ranges) VM_CUDA(cudaMemsetAsync(lane.d_node_rank.p, 0xFF, sizeof(int32_t) * node_total, s));
+
+    if (any_device_lookup) {
+        int32_t max_bsp = 0;
+        for (int f = f0; f < f1; ++f)
+            if (frames[f].ranges == nullptr) max_bsp = std::max(max_bsp, frames[f].mesh->n_bsp);
+        dim3 g((max_bsp + SELECT_THREADS - 1) / SELECT_THREADS, nf);
+        begin_stage(e, s, "bsp_state");
+        k_bsp_state<<<g, SELECT_THREADS, 0, s>>>(lane.d_frames.p, lane.d_state.p);
+        VM_CUDA(cudaGetLastError());
+        end_stage(e, s);
+    }
+    {
+        dim3 g(blocks_per_frame, nf);
+        begin_stage(e, s, "select_project");
+        k_select<<<g, SELECT_THREADS, 0, s>>>(lane.d_frames.p, lane.d_state.p, lane.d_cand_px.p, lane.d_cand_node.p,
+                                              lane.d_block_counts.p, e->d_abort);
+        VM_CUDA(cudaGetLastError());
+        end_stage(e, s);
+    }
+    // the scan continues the batch-wide offsets from the previous chunk's scan
+    if (prev != nullptr && prev != &lane) VM_CUDA(cudaStreamWaitEvent(s, prev->ev_scan, 0));
+    begin_stage(e, s, "scan");
+    k_scan<<<1, 1024, 0, s>>>(lane.d_block_counts.p, n_blocks, blocks_per_frame, nf, e->d_offsets.p, f0);
+    VM_CUDA(cudaGetLastError());
+    end_stage(e, s);
+    VM_CUDA(cudaEventRecord(lane.ev_scan, s));
+    VM_CUDA(cudaMemcpyAsync(e->h_offsets.p + f0 + 1, e->d_offsets.p + f0 + 1, sizeof(int32_t) * nf, cudaMemcpyDeviceToHost, s));
+    VM_CUDA(cudaEventRecord(lane.ev_offsets, s));
+    {
+        dim3 g(blocks_per_frame, nf);
+        begin_stage(e, s, "scatter_compact");
+        k_scatter<<<g, SELECT_THREADS, 0, s>>>(lane.d_frames.p, lane.d_cand_px.p, lane.d_cand_node.p, lane.d_block_counts.p,
+                                               e->d_offsets.p, f0, e->d_px.p, e->d_gi.p, lane.d_node_rank.p);
+        VM_CUDA(cudaGetLastError());
+        end_stage(e, s);
+    }
+    const int max_rows = max_cand + 1;
+    {
+        dim3 g((max_rows + ROW_THREADS - 1) / ROW_THREADS, nf);
+        const int N = frames[f0].mesh->n_neighbours;
+        begin_stage(e, s, "remap_neighbours");
+        if (N == 4) k_remap<4><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_gi.p, lane.d_node_rank.p, e->d_nb.p);
+        else if (N == 6) k_remap<6><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_gi.p, lane.d_node_rank.p, e->d_nb.p);
+        else k_remap<8><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_gi.p, lane.d_node_rank.p, e->d_nb.p);
+        VM_CUDA(cudaGetLastError());
+        end_stage(e, s);
+        if (classify) {
+            begin_stage(e, s, "sample_image");
+            k_sample<<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_px.p,
+                                               reinterpret_cast<float4*>(lane.d_feat[0].p));
+            VM_CUDA(cudaGetLastError());
+            end_stage(e, s);
+            run_network(e, lane, e->d_offsets.p, e->d_nb.p, N, f0, nf, max_rows, e->d_cls.p, true);
+        }
+    }
+    lane.busy = true;
+}
+
+// Copies a finished chunk's results to the host. Needs the chunk's offsets on the host first.
+static void enqueue_chunk_readback(vm_engine* e, Lane& lane, int N, bool classify, bool to_host) {
+    VM_CUDA(cudaEventSynchronize(lane.ev_offsets));
+    if (to_host) {
+        const int32_t* off = e->h_offsets.p;
+        const size_t p0 = off[lane.f0], p1 = off[lane.f1];
+        const size_t r0 = p0 + lane.f0, r1 = p1 + lane.f1;
+        cudaStream_t s = lane.stream;
+        if (p1 > p0) {
+            VM_CUDA(cudaMemcpyAsync(e->h_px.p + p0, e->d_px.p + p0, sizeof(float2) * (p1 - p0), cudaMemcpyDeviceToHost, s));
+            VM_CUDA(cudaMemcpyAsync(e->h_gi.p + p0, e->d_gi.p + p0, sizeof(int32_t) * (p1 - p0), cudaMemcpyDeviceToHost, s));
+        }
+        VM_CUDA(cudaMemcpyAsync(e->h_nb.p + r0 * N, e->d_nb.p + r0 * N, sizeof(int32_t) * (r1 - r0) * N, cudaMemcpyDeviceToHost, s));
+        if (classify) {
+            const size_t C = e->n_classes;
+            VM_CUDA(cudaMemcpyAsync(e->h_cls.p + r0 * C, e->d_cls.p + r0 * C, sizeof(float) * (r1 - r0) * C, cudaMemcpyDeviceToHost, s));
+        }
+    }
+    VM_CUDA(cudaEventRecord(lane.ev_done, lane.stream));
+}
+
+static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frames, uint32_t flags, vm_batch_result* out) {
+    if (e == nullptr || out == nullptr || n_frames < 0 || (n_frames > 0 && frames == nullptr)) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "null engine, frames or result");
+    }
+    std::memset(out, 0, sizeof(*out));
+    if (n_frames == 0) return VM_OK;
+
+    // validation, before any device work - the reference throws from inside the call for the same conditions
+    bool classify = frames[0].image != nullptr && !e->layers.empty();
+    const int N   = frames[0].mesh != nullptr ? frames[0].mesh->n_neighbours : 0;
+    int64_t cand_all = 0;
+    for (int f = 0; f < n_frames; ++f) {
+        const vm_frame& fr = frames[f];
+        if (fr.mesh == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "frame without a mesh");
+        if (fr.mesh->n_neighbours != N) return fail(VM_ERR_INVALID_ARGUMENT, "frames of one batch must share n_neighbours");
+        if (fr.lens.projection != VM_RECTILINEAR && fr.lens.projection != VM_EQUISOLID && fr.lens.projection != VM_EQUIDISTANT) {
+            return fail(VM_ERR_UNSUPPORTED_LENS, "Cannot project: Unknown lens type");
+        }
+        if (fr.lens.dimensions[0] <= 0 || fr.lens.dimensions[1] <= 0) return fail(VM_ERR_INVALID_ARGUMENT, "lens dimensions must be positive");
+        if (fr.ranges == nullptr && fr.n_ranges != 0) return fail(VM_ERR_INVALID_ARGUMENT, "n_ranges without ranges");
+        if (fr.ranges == nullptr && fr.mesh->n_bsp == 0) return fail(VM_ERR_NO_BSP, "device lookup needs vm_mesh_set_bsp");
+        if (fr.n_ranges < 0) return fail(VM_ERR_INVALID_ARGUMENT, "negative n_ranges");
+        for (int r = 0; r < fr.n_ranges; ++r) {
+            if (fr.ranges[2 * r] < 0 || fr.ranges[2 * r + 1] > fr.mesh->n_nodes || fr.ranges[2 * r] > fr.ranges[2 * r + 1]) {
+                return fail(VM_ERR_INVALID_ARGUMENT, "range outside the mesh");
+            }
+        }
+        if ((fr.image != nullptr) != (frames[0].image != nullptr)) return fail(VM_ERR_INVALID_ARGUMENT, "either all frames carry an image or none");
+        if (classify && format_class(fr.format) == FMT_UNKNOWN) {
+            char code[5] = {char(fr.format & 0xFF), char(fr.format >> 8 & 0xFF), char(fr.format >> 16 & 0xFF), char(fr.format >> 24 & 0xFF), 0};
+            return fail(VM_ERR_UNSUPPORTED_FORMAT, std::string("Unsupported image format ") + code);
+        }
+        cand_all += frame_candidates(fr);
+    }
+    if (classify && e->layers.front().cin != 4) return fail(VM_ERR_NETWORK_SHAPE, "first layer must take 4 channels");
+    if (classify && e->layers.front().n_slots != N + 1) return fail(VM_ERR_NETWORK_SHAPE, "network was built for a different n_neighbours");
+    if (cand_all + n_frames > (int64_t(1) << 31) - 1024) return fail(VM_ERR_INVALID_ARGUMENT, "batch too large: split it");
+
+    try {
+        VM_CUDA(cudaSetDevice(e->device));
+        e->timing = (flags & VM_TIME_STAGES) != 0;
+        e->timers.clear();
+        e->events_used = 0;
+        e->stage_ms.clear();
+        const bool to_host = (flags & VM_RESULTS_ON_DEVICE) == 0;
+        const int n_lanes  = e->timing ? 1 : e->n_lanes;
+
+        const size_t rows_all = static_cast<size_t>(cand_all) + n_frames;
+        e->d_offsets.ensure(n_frames + 1);
+        e->h_offsets.ensure(n_frames + 1);
+        e->d_px.ensure(cand_all + 1);
+        e->d_gi.ensure(cand_all + 1);
+        e->d_nb.ensure(rows_all * N);
+        if (classify) e->d_cls.ensure(rows_all * e->n_classes);
+        if (to_host) {
+            e->h_px.ensure(cand_all + 1);
+            e->h_gi.ensure(cand_all + 1);
+            e->h_nb.ensure(rows_all * N);
+            if (classify) e->h_cls.ensure(rows_all * e->n_classes);
+        }
+        e->h_offsets.p[0] = 0;
+        *e->h_abort       = 0;
+        VM_CUDA(cudaMemsetAsync(e->d_offsets.p, 0, sizeof(int32_t), e->lanes[0].stream));
+        VM_CUDA(cudaMemsetAsync(e->d_abort, 0, sizeof(int32_t), e->lanes[0].stream));
+
+        // chunks: runs of frames bounded by a candidate budget and a frame count
+        int f0 = 0, chunk = 0;
+        Lane* prev = nullptr;
+        std::vector<Lane*> order;
+        while (f0 < n_frames) {
+            int f1 = f0;
+            int64_t c = 0;
+            while (f1 < n_frames && (f1 == f0 || (c + frame_candidates(frames[f1]) <= e->chunk_candidates && f1 - f0 < e->chunk_frames))) {
+                c += frame_candidates(frames[f1]);
+                ++f1;
+            }
+            Lane& lane = e->lanes[chunk % n_lanes];
+            if (lane.busy) {
+                // its previous chunk must have left the lane's staging and scratch
+                VM_CUDA(cudaEventSynchronize(lane.ev_done));
+                lane.busy = false;
+            }
+            enqueue_chunk(e, lane, prev, frames, f0, f1, classify);
+            // while this chunk runs, read back the one before it
+            if (prev != nullptr) enqueue_chunk_readback(e, *prev, N, classify, to_host);
+            if (n_lanes == 1) {
+                enqueue_chunk_readback(e, lane, N, classify, to_host);
+                prev = nullptr;
+                // a single lane still has to chain its scans: same stream, already ordered
+            }
+            else {
+                prev = &lane;
+            }
+            f0 = f1;
+            ++chunk;
+        }
+        if (prev != nullptr) enqueue_chunk_readback(e, *prev, N, classify, to_host);
+        VM_CUDA(cudaMemcpyAsync(e->h_abort, e->d_abort, sizeof(int32_t), cudaMemcpyDeviceToHost, e->lanes[(chunk - 1) % n_lanes].stream));
+        for (int l = 0; l < n_lanes; ++l) {
+            VM_CUDA(cudaStreamSynchronize(e->lanes[l].stream));
+            e->lanes[l].busy = false;
+        }
+        if (*e->h_abort != 0) return fail(VM_ERR_DEVICE_ABORT, "a kernel gave up on a bounded loop (BSP deeper than 128 levels)");
+
+        if (e->timing) {
+            for (const auto& t : e->timers) {
+                float ms = 0.0f;
+                VM_CUDA(cudaEventElapsedTime(&ms, t.start, t.stop));
+                e->stage_ms.emplace_back(t.name, ms);
+            }
+        }
+
+        out->n_frames     = n_frames;
+        out->n_neighbours = N;
+        out->n_classes    = classify ? e->n_classes : 0;
+        out->on_device    = to_host ? 0 : 1;
+        out->offsets      = e->h_offsets.p;
+        if (to_host) {
+            out->pixel_coordinates = reinterpret_cast<const float*>(e->h_px.p);
+            out->global_indices    = e->h_gi.p;
+            out->neighbourhood     = e->h_nb.p;
+            out->classifications   = classify ? e->h_cls.p : nullptr;
+        }
+        else {
+            out->pixel_coordinates = reinterpret_cast<const float*>(e->d_px.p);
+            out->global_indices    = e->d_gi.p;
+            out->neighbourhood     = e->d_nb.p;
+            out->classifications   = classify ? e->d_cls.p : nullptr;
+        }
+        return VM_OK;
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        const vm_status s = f.code == cudaErrorMemoryAllocation ? VM_ERR_OUT_OF_MEMORY : VM_ERR_CUDA;
+        return fail(s, std::string(cudaGetErrorName(f.code)) + ": " + cudaGetErrorString(f.code) + " in " + f.what);
+    }
+}
+
+}  // namespace vm
+
+using namespace vm;
+
+extern "C" {
+
+const char* vm_last_error(void) {
+    return g_error.c_str();
+}
+
+// lets the host mesh translation unit report through the same per-thread message
+void vm_set_last_error_(const char* message) {
+    g_error = message != nullptr ? message : "";
+}
+
+vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* layers_per_group, int32_t n_groups, vm_engine** out) {
+    if (out == nullptr || n_groups < 0 || (n_groups > 0 && (layers == nullptr || layers_per_group == nullptr))) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "null argument");
+    }
+    *out = nullptr;
+    // shape check: cpp/visualmesh/engine/cpu/engine.hpp:213-256 multiplies whatever it is given; a mismatch there is
+    // undefined behaviour, here it is an error
+    {
+        int l = 0, width = 4, slots_first = 0;
+        for (int g = 0; g < n_groups; ++g) {
+            if (layers_per_group[g] <= 0) return fail(VM_ERR_NETWORK_SHAPE, "a group needs at least one layer");
+            for (int i = 0; i < layers_per_group[g]; ++i, ++l) {
+                const vm_layer& L = layers[l];
+                if (L.weights == nullptr || L.biases == nullptr || L.n_in <= 0 || L.n_out <= 0) return fail(VM_ERR_NETWORK_SHAPE, "empty layer");
+                if (L.activation < VM_SELU || L.activation > VM_TANH) return fail(VM_ERR_NETWORK_SHAPE, "unknown activation");
+                if (i == 0) {
+                    if (L.n_in % width != 0) return fail(VM_ERR_NETWORK_SHAPE, "gather layer rows must be (N+1) x previous width");
+                    const int slots = L.n_in / width;
+                    if (slots != 5 && slots != 7 && slots != 9) return fail(VM_ERR_NETWORK_SHAPE, "gather layer rows must be (N+1) x previous width, N in {4,6,8}");
+                    if (slots_first == 0) slots_first = slots;
+                    if (slots != slots_first) return fail(VM_ERR_NETWORK_SHAPE, "all groups must gather the same number of neighbours");
+                }
+                else if (L.n_in != width) {
+                    return fail(VM_ERR_NETWORK_SHAPE, "dense layer rows must equal the previous width");
+                }
+                width = L.n_out;
+            }
+        }
+    }
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(VM_ERR_CUDA, "no CUDA device: this engine has no CPU fallback");
+    }
+    std::unique_ptr<vm_engine> e(new vm_engine());
+    try {
+        if (device < 0) VM_CUDA(cudaGetDevice(&device));
+        if (device >= count) return fail(VM_ERR_INVALID_ARGUMENT, "no such device");
+        e->device = device;
+        VM_CUDA(cudaSetDevice(device));
+        if (const char* v = std::getenv("VMCUDA_CHUNK_FRAMES")) e->chunk_frames = std::max(1, std::atoi(v));
+        if (const char* v = std::getenv("VMCUDA_CHUNK_CANDIDATES")) e->chunk_candidates = std::max<long long>(1, std::atoll(v));
+        if (const char* v = std::getenv("VMCUDA_LANES")) e->n_lanes = std::min(MAX_LANES, std::max(1, std::atoi(v)));
+        for (int l = 0; l < MAX_LANES; ++l) {
+            Lane& lane = e->lanes[l];
+            VM_CUDA(cudaStreamCreateWithFlags(&lane.stream, cudaStreamNonBlocking));
+            VM_CUDA(cudaEventCreateWithFlags(&lane.ev_staged, cudaEventDisableTiming));
+            VM_CUDA(cudaEventCreateWithFlags(&lane.ev_scan, cudaEventDisableTiming));
+            VM_CUDA(cudaEventCreateWithFlags(&lane.ev_offsets, cudaEventDisableTiming));
+            VM_CUDA(cudaEventCreateWithFlags(&lane.ev_done, cudaEventDisableTiming));
+        }
+        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&e->d_abort), sizeof(int32_t)));
+        VM_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&e->h_abort), sizeof(int32_t), cudaHostAllocDefault));
+        int l = 0;
+        int width = 4;
+        for (int g = 0; g < n_groups; ++g) {
+            for (int i = 0; i < layers_per_group[g]; ++i, ++l) {
+                const vm_layer& L = layers[l];
+                DenseLayer d;
+                d.n_slots    = i == 0 ? L.n_in / width : 1;
+                d.cin        = width;
+                d.cout       = L.n_out;
+                d.coutp      = (L.n_out + 3) & ~3;
+                d.activation = L.activation;
+                // [n_in][n_out] as handed over (cpp/visualmesh/network_structure.hpp:25-27), padded to coutp columns
+                std::vector<float> packed((static_cast<size_t>(L.n_in) + 1) * d.coutp, 0.0f);
+                for (int r = 0; r < L.n_in; ++r)
+                    for (int c = 0; c < L.n_out; ++c) packed[static_cast<size_t>(r) * d.coutp + c] = L.weights[static_cast<size_t>(r) * L.n_out + c];
+                for (int c = 0; c < L.n_out; ++c) packed[static_cast<size_t>(L.n_in) * d.coutp + c] = L.biases[c];
+                VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&d.d_weights), packed.size() * sizeof(float)));
+                VM_CUDA(cudaMemcpy(d.d_weights, packed.data(), packed.size() * sizeof(float), cudaMemcpyHostToDevice));
+                e->layers.push_back(d);
+                width        = L.n_out;
+                e->max_width = std::max(e->max_width, width);
+            }
+        }
+        e->n_classes = e->layers.empty() ? 0 : e->layers.back().cout;
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        return fail(f.code == cudaErrorMemoryAllocation ? VM_ERR_OUT_OF_MEMORY : VM_ERR_CUDA,
+                    std::string(cudaGetErrorName(f.code)) + " in " + f.what);
+    }
+    *out = e.release();
+    return VM_OK;
+}
+
+static void free_mesh(vm_mesh* m) {
+    if (m == nullptr) return;
+    cudaFree(m->d_rays);
+    cudaFree(m->d_neighbours);
+    cudaFree(m->d_cones_a);
+    cudaFree(m->d_cones_s);
+    cudaFree(m->d_topology);
+    delete m;
+}
+
+void vm_engine_destroy(vm_engine* e) {
+    if (e == nullptr) return;
+    cudaSetDevice(e->device);
+    cudaDeviceSynchronize();
+    for (auto* m : e->meshes) free_mesh(m);
+    for (auto& L : e->layers) cudaFree(L.d_weights);
+    for (auto& lane : e->lanes) {
+        lane.h_frames.release();
+        lane.d_frames.release();
+        lane.h_ranges.release();
+        lane.d_ranges.release();
+        lane.d_state.release();
+        lane.d_cand_px.release();
+        lane.d_cand_node.release();
+        lane.d_block_counts.release();
+        lane.d_node_rank.release();
+        lane.d_feat[0].release();
+        lane.d_feat[1].release();
+        lane.d_images.release();
+        if (lane.stream) cudaStreamDestroy(lane.stream);
+        if (lane.ev_staged) cudaEventDestroy(lane.ev_staged);
+        if (lane.ev_scan) cudaEventDestroy(lane.ev_scan);
+        if (lane.ev_offsets) cudaEventDestroy(lane.ev_offsets);
+        if (lane.ev_done) cudaEventDestroy(lane.ev_done);
+    }
+    e->d_offsets.release();
+    e->h_offsets.release();
+    e->d_px.release();
+    e->d_gi.release();
+    e->d_nb.release();
+    e->d_cls.release();
+    e->h_px.release();
+    e->h_gi.release();
+    e->h_nb.release();
+    e->h_cls.release();
+    for (auto ev : e->event_pool) cudaEventDestroy(ev);
+    cudaFree(e->d_abort);
+    cudaFreeHost(e->h_abort);
+    delete e;
+}
+
+vm_status vm_mesh_upload(vm_engine* e, const float* rays, const int32_t* neighbours, int32_t n_nodes, int32_t n_neighbours, vm_mesh** out) {
+    if (e == nullptr || rays == nullptr || neighbours == nullptr || out == nullptr || n_nodes <= 0) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "null argument or empty mesh");
+    }
+    if (n_neighbours != 4 && n_neighbours != 6 && n_neighbours != 8) return fail(VM_ERR_INVALID_ARGUMENT, "n_neighbours must be 4, 6 or 8");
+    *out = nullptr;
+    std::unique_ptr<vm_mesh> m(new vm_mesh());
+    try {
+        VM_CUDA(cudaSetDevice(e->device));
+        m->n_nodes      = n_nodes;
+        m->n_neighbours = n_neighbours;
+        // rays padded to float4 as the OpenCL engine does (cpp/visualmesh/engine/opencl/engine.hpp:611-615)
+        std::vector<float4> padded(n_nodes);
+        for (int i = 0; i < n_nodes; ++i) padded[i] = make_float4(rays[3 * i], rays[3 * i + 1], rays[3 * i + 2], 0.0f);
+        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->d_rays), sizeof(float4) * n_nodes));
+        VM_CUDA(cudaMemcpy(m->d_rays, padded.data(), sizeof(float4) * n_nodes, cudaMemcpyHostToDevice));
+        const size_t nb_bytes = sizeof(int32_t) * static_cast<size_t>(n_nodes) * n_neighbours;
+        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->d_neighbours), nb_bytes));
+        VM_CUDA(cudaMemcpy(m->d_neighbours, neighbours, nb_bytes, cudaMemcpyHostToDevice));
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        free_mesh(m.release());
+        return fail(f.code == cudaErrorMemoryAllocation ? VM_ERR_OUT_OF_MEMORY : VM_ERR_CUDA, std::string(cudaGetErrorName(f.code)) + " in " + f.what);
+    }
+    e->meshes.push_back(m.get());
+    *out = m.release();
+    return VM_OK;
+}
+
+vm_status vm_mesh_set_bsp(vm_engine* e, vm_mesh* m, int32_t n, const int32_t* ranges, const int32_t* children, const float* cones) {
+    if (e == nullptr || m == nullptr || n <= 0 || ranges == nullptr || children == nullptr || cones == nullptr) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "null argument or empty BSP");
+    }
+    std::vector<float4> a(n);
+    std::vector<float> s(n);
+    std::vector<int4> t(n);
+    for (int i = 0; i < n; ++i) {
+        a[i] = make_float4(cones[5 * i], cones[5 * i + 1], cones[5 * i + 2], cones[5 * i + 3]);
+        s[i] = cones[5 * i + 4];
+        const int c0 = children[2 * i], c1 = children[2 * i + 1];
+        if (c0 >= n || c1 >= n || (c0 < 0) != (c1 < 0)) return fail(VM_ERR_INVALID_ARGUMENT, "BSP child out of range");
+        if (ranges[2 * i] < 0 || ranges[2 * i + 1] > m->n_nodes) return fail(VM_ERR_INVALID_ARGUMENT, "BSP range outside the mesh");
+        t[i] = make_int4(c0, c1, c1 >= 0 ? ranges[2 * c1] : 0, 0);
+    }
+    try {
+        VM_CUDA(cudaSetDevice(e->device));
+        cudaFree(m->d_cones_a);
+        cudaFree(m->d_cones_s);
+        cudaFree(m->d_topology);
+        m->d_cones_a = nullptr;
+        m->d_cones_s = nullptr;
+        m->d_topology = nullptr;
+        m->n_bsp = 0;
+        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->d_cones_a), sizeof(float4) * n));
+        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->d_cones_s), sizeof(float) * n));
+        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&m->d_topology), sizeof(int4) * n));
+        VM_CUDA(cudaMemcpy(m->d_cones_a, a.data(), sizeof(float4) * n, cudaMemcpyHostToDevice));
+        VM_CUDA(cudaMemcpy(m->d_cones_s, s.data(), sizeof(float) * n, cudaMemcpyHostToDevice));
+        VM_CUDA(cudaMemcpy(m->d_topology, t.data(), sizeof(int4) * n, cudaMemcpyHostToDevice));
+        m->n_bsp = n;
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        return fail(f.code == cudaErrorMemoryAllocation ? VM_ERR_OUT_OF_MEMORY : VM_ERR_CUDA, std::string(cudaGetErrorName(f.code)) + " in " + f.what);
+    }
+    return VM_OK;
+}
+
+void vm_mesh_release(vm_engine* e, vm_mesh* m) {
+    if (e == nullptr || m == nullptr) return;
+    cudaSetDevice(e->device);
+    cudaDeviceSynchronize();
+    e->meshes.erase(std::remove(e->meshes.begin(), e->meshes.end(), m), e->meshes.end());
+    free_mesh(m);
+}
+
+vm_status vm_run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frames, uint32_t flags, vm_batch_result* out) {
+    return run_batch(e, frames, n_frames, flags, out);
+}
+
+vm_status vm_project(vm_engine* e, const vm_mesh* mesh, const int32_t* ranges, int32_t n_ranges, const float Hoc[16], const vm_lens* lens, vm_batch_result* out) {
+    if (Hoc == nullptr || lens == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "null Hoc or lens");
+    vm_frame fr{};
+    fr.mesh     = mesh;
+    fr.ranges   = ranges;
+    fr.n_ranges = n_ranges;
+    std::memcpy(fr.Hoc, Hoc, sizeof(fr.Hoc));
+    fr.lens = *lens;
+    return run_batch(e, &fr, 1, 0, out);
+}
+
+vm_status vm_classify(vm_engine* e, const vm_mesh* mesh, const int32_t* ranges, int32_t n_ranges, const float Hoc[16], const vm_lens* lens, const void* image, uint32_t format, vm_batch_result* out) {
+    if (Hoc == nullptr || lens == nullptr || image == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "null Hoc, lens or image");
+    if (e != nullptr && e->layers.empty()) return fail(VM_ERR_NETWORK_SHAPE, "this engine was created without a network");
+    vm_frame fr{};
+    fr.mesh     = mesh;
+    fr.ranges   = ranges;
+    fr.n_ranges = n_ranges;
+    std::memcpy(fr.Hoc, Hoc, sizeof(fr.Hoc));
+    fr.lens   = *lens;
+    fr.image  = image;
+    fr.format = format;
+    return run_batch(e, &fr, 1, 0, out);
+}
+
+vm_status vm_sample(vm_engine* e, const float* px, int32_t n, const void* image, int32_t width, int32_t height, uint32_t format, float* out) {
+    if (e == nullptr || px == nullptr || image == nullptr || out == nullptr || n < 0 || width <= 0 || height <= 0) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "null argument");
+    }
+    const int cls = format_class(format);
+    if (cls == FMT_UNKNOWN) return fail(VM_ERR_UNSUPPORTED_FORMAT, "Unsupported image format");
+    if (n == 0) return VM_OK;
+    try {
+        VM_CUDA(cudaSetDevice(e->device));
+        Lane& lane        = e->lanes[0];
+        const size_t bytes = static_cast<size_t>(width) * height * format_bytes_per_pixel(cls);
+        lane.d_images.ensure(bytes);
+        lane.d_cand_px.ensure(n);
+        lane.d_feat[0].ensure(static_cast<size_t>(n) * 4);
+        VM_CUDA(cudaMemcpyAsync(lane.d_images.p, image, bytes, cudaMemcpyHostToDevice, lane.stream));
+        VM_CUDA(cudaMemcpyAsync(lane.d_cand_px.p, px, sizeof(float2) * n, cudaMemcpyHostToDevice, lane.stream));
+        ++e->launches;
+        k_sample_flat<<<(n + ROW_THREADS - 1) / ROW_THREADS, ROW_THREADS, 0, lane.stream>>>(
+          lane.d_cand_px.p, n, lane.d_images.p, width, height, cls, reinterpret_cast<float4*>(lane.d_feat[0].p));
+        VM_CUDA(cudaGetLastError());
+        VM_CUDA(cudaMemcpyAsync(out, lane.d_feat[0].p, sizeof(float) * 4 * n, cudaMemcpyDeviceToHost, lane.stream));
+        VM_CUDA(cudaStreamSynchronize(lane.stream));
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        return fail(f.code == cudaErrorMemoryAllocation ? VM_ERR_OUT_OF_MEMORY : VM_ERR_CUDA, std::string(cudaGetErrorName(f.code)) + " in " + f.what);
+    }
+    return VM_OK;
+}
+
+vm_status vm_network(vm_engine* e, const float* input, const int32_t* neighbourhood, int32_t n_rows, int32_t n_neighbours, float* out) {
+    if (e == nullptr || input == nullptr || neighbourhood == nullptr || out == nullptr || n_rows <= 0) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "null argument");
+    }
+    if (e->layers.empty()) return fail(VM_ERR_NETWORK_SHAPE, "this engine was created without a network");
+    if (e->layers.front().n_slots != n_neighbours + 1) return fail(VM_ERR_NETWORK_SHAPE, "network was built for a different n_neighbours");
+    for (size_t i = 0; i < static_cast<size_t>(n_rows) * n_neighbours; ++i) {
+        if (neighbourhood[i] < 0 || neighbourhood[i] >= n_rows) return fail(VM_ERR_INVALID_ARGUMENT, "neighbour index outside the rows");
+    }
+    try {
+        VM_CUDA(cudaSetDevice(e->device));
+        Lane& lane = e->lanes[0];
+        const size_t rows = n_rows;
+        e->d_offsets.ensure(2);
+        e->d_nb.ensure(rows * n_neighbours);
+        e->d_cls.ensure(rows * e->n_classes);
+        lane.d_feat[0].ensure(rows * e->max_width);
+        lane.d_feat[1].ensure(rows * e->max_width);
+        const int32_t offsets[2] = {0, n_rows - 1};
+        VM_CUDA(cudaMemcpyAsync(e->d_offsets.p, offsets, sizeof(offsets), cudaMemcpyHostToDevice, lane.stream));
+        VM_CUDA(cudaMemcpyAsync(e->d_nb.p, neighbourhood, sizeof(int32_t) * rows * n_neighbours, cudaMemcpyHostToDevice, lane.stream));
+        VM_CUDA(cudaMemcpyAsync(lane.d_feat[0].p, input, sizeof(float) * rows * 4, cudaMemcpyHostToDevice, lane.stream));
+        e->timing = false;
+        run_network(e, lane, e->d_offsets.p, e->d_nb.p, n_neighbours, 0, 1, n_rows, e->d_cls.p, true);
+        VM_CUDA(cudaMemcpyAsync(out, e->d_cls.p, sizeof(float) * rows * e->n_classes, cudaMemcpyDeviceToHost, lane.stream));
+        VM_CUDA(cudaStreamSynchronize(lane.stream));
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        return fail(f.code == cudaErrorMemoryAllocation ? VM_ERR_OUT_OF_MEMORY : VM_ERR_CUDA, std::string(cudaGetErrorName(f.code)) + " in " + f.what);
+    }
+    return VM_OK;
+}
+
+vm_status vm_stage_times(vm_engine* e, const char** names, float* ms, int32_t capacity, int32_t* n) {
+    if (e == nullptr || n == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "null argument");
+    *n = static_cast<int32_t>(e->stage_ms.size());
+    for (int i = 0; i < *n && i < capacity; ++i) {
+        if (names != nullptr) names[i] = e->stage_ms[i].first;
+        if (ms != nullptr) ms[i] = e->stage_ms[i].second;
+    }
+    return VM_OK;
+}
+
+int64_t vm_launch_count(const vm_engine* e) {
+    return e == nullptr ? 0 : e->launches;
+}
+
+vm_status vm_host_alloc(void** ptr, size_t bytes) {
+    if (ptr == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "null argument");
+    const cudaError_t err = cudaHostAlloc(ptr, bytes, cudaHostAllocDefault);
+    if (err != cudaSuccess) {
+        cudaGetLastError();
+        return fail(err == cudaErrorMemoryAllocation ? VM_ERR_OUT_OF_MEMORY : VM_ERR_CUDA, cudaGetErrorString(err));
+    }
+    return VM_OK;
+}
+
+void vm_host_free(void* ptr) {
+    if (ptr != nullptr) cudaFreeHost(ptr);
+}
+
+}  // extern "C"
