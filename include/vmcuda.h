@@ -190,6 +190,12 @@ VM_API vm_status vm_network(vm_engine* engine,
  * Returns the number of stages through *n; names[i] points at a static string. */
 VM_API vm_status vm_stage_times(vm_engine* engine, const char** names, float* milliseconds, int32_t capacity, int32_t* n);
 
+/* Device-side stopwatch over any number of calls: vm_timer_start records a CUDA event on the engine's first stream
+ * (after draining its streams), vm_timer_stop records one that follows all of the engine's streams, waits for it and
+ * returns the elapsed device time. */
+VM_API vm_status vm_timer_start(vm_engine* engine);
+VM_API vm_status vm_timer_stop(vm_engine* engine, float* milliseconds);
+
 /* Number of kernels launched by this engine since creation. */
 VM_API int64_t vm_launch_count(const vm_engine* engine);
 

@@ -83,6 +83,8 @@ SYMBOLS = {
     "vm_network": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "vm_stage_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_char_p), C.POINTER(C.c_float), C.c_int32,
                                  C.POINTER(C.c_int32)]),
+    "vm_timer_start": (C.c_int, [C.c_void_p]),
+    "vm_timer_stop": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "vm_launch_count": (C.c_int64, [C.c_void_p]),
     "vm_host_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
     "vm_host_free": (None, [C.c_void_p]),

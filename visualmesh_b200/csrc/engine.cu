@@ -83,6 +83,7 @@ struct PinnedArray {
 struct DenseLayer {
     float* d_weights = nullptr;  // [n_slots * cin][coutp] then [coutp] biases
     int cin = 0, cout = 0, coutp = 0, n_slots = 1, activation = 0;
+    std::string stage;  // name under which this layer's kernel is timed, e.g. "graph_conv_16x16"
 };
 
 constexpr int MAX_LANES = 3;
@@ -154,6 +155,7 @@ struct vm_engine {
     bool timing        = false;
     std::vector<std::pair<const char*, float>> stage_ms;
     int64_t launches = 0;
+    cudaEvent_t ev_timer_start = nullptr, ev_timer_stop = nullptr;
 };
 
 namespace vm {
@@ -216,7 +218,7 @@ static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_fra
     a.n_slots     = L.n_slots;
     a.activation  = L.activation;
     dim3 grid(1, n_frames);
-    begin_stage(e, s, "graph_conv");
+    begin_stage(e, s, L.stage.c_str());
     if (!launch_conv_fast(L, a, grid, max_rows, s)) {
         dim3 g((max_rows + CONV_THREADS - 1) / CONV_THREADS, n_frames);
         k_graph_conv_generic<<<g, CONV_THREADS, 0, s>>>(a, L.cin, L.cout, L.coutp);
@@ -695,6 +697,8 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
             VM_CUDA(cudaEventCreateWithFlags(&lane.ev_offsets, cudaEventDisableTiming));
             VM_CUDA(cudaEventCreateWithFlags(&lane.ev_done, cudaEventDisableTiming));
         }
+        VM_CUDA(cudaEventCreate(&e->ev_timer_start));
+        VM_CUDA(cudaEventCreate(&e->ev_timer_stop));
         VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&e->d_abort), sizeof(int32_t)));
         VM_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&e->h_abort), sizeof(int32_t), cudaHostAllocDefault));
         int l = 0;
@@ -708,6 +712,7 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
                 d.cout       = L.n_out;
                 d.coutp      = (L.n_out + 3) & ~3;
                 d.activation = L.activation;
+                d.stage      = std::string(i == 0 ? "graph_conv_" : "dense_") + std::to_string(width) + "x" + std::to_string(L.n_out);
                 // [n_in][n_out] as handed over (cpp/visualmesh/network_structure.hpp:25-27), padded to coutp columns
                 std::vector<float> packed((static_cast<size_t>(L.n_in) + 1) * d.coutp, 0.0f);
                 for (int r = 0; r < L.n_in; ++r)
@@ -777,6 +782,8 @@ void vm_engine_destroy(vm_engine* e) {
     e->h_nb.release();
     e->h_cls.release();
     for (auto ev : e->event_pool) cudaEventDestroy(ev);
+    if (e->ev_timer_start) cudaEventDestroy(e->ev_timer_start);
+    if (e->ev_timer_stop) cudaEventDestroy(e->ev_timer_stop);
     cudaFree(e->d_abort);
     cudaFreeHost(e->h_abort);
     delete e;
@@ -958,6 +965,40 @@ vm_status vm_stage_times(vm_engine* e, const char** names, float* ms, int32_t ca
     for (int i = 0; i < *n && i < capacity; ++i) {
         if (names != nullptr) names[i] = e->stage_ms[i].first;
         if (ms != nullptr) ms[i] = e->stage_ms[i].second;
+    }
+    return VM_OK;
+}
+
+vm_status vm_timer_start(vm_engine* e) {
+    if (e == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "null engine");
+    try {
+        VM_CUDA(cudaSetDevice(e->device));
+        for (int l = 0; l < MAX_LANES; ++l) VM_CUDA(cudaStreamSynchronize(e->lanes[l].stream));
+        VM_CUDA(cudaEventRecord(e->ev_timer_start, e->lanes[0].stream));
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        return fail(VM_ERR_CUDA, std::string(cudaGetErrorName(f.code)) + " in " + f.what);
+    }
+    return VM_OK;
+}
+
+vm_status vm_timer_stop(vm_engine* e, float* milliseconds) {
+    if (e == nullptr || milliseconds == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "null argument");
+    try {
+        VM_CUDA(cudaSetDevice(e->device));
+        // lane 0 waits for the other lanes, then stamps the end
+        for (int l = 1; l < MAX_LANES; ++l) {
+            VM_CUDA(cudaEventRecord(e->lanes[l].ev_staged, e->lanes[l].stream));
+            VM_CUDA(cudaStreamWaitEvent(e->lanes[0].stream, e->lanes[l].ev_staged, 0));
+        }
+        VM_CUDA(cudaEventRecord(e->ev_timer_stop, e->lanes[0].stream));
+        VM_CUDA(cudaEventSynchronize(e->ev_timer_stop));
+        VM_CUDA(cudaEventElapsedTime(milliseconds, e->ev_timer_start, e->ev_timer_stop));
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        return fail(VM_ERR_CUDA, std::string(cudaGetErrorName(f.code)) + " in " + f.what);
     }
     return VM_OK;
 }

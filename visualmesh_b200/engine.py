@@ -272,7 +272,9 @@ class Engine:
         self._meshes[id(mesh)] = (mesh, handle)
         return handle
 
-    def run_batch(self, frames: Sequence[FrameInput], results_on_device=False, time_stages=False) -> BatchResult:
+    def prepare_batch(self, frames: Sequence[FrameInput]):
+        """Marshals frames into the C ABI's vm_frame array once; the result can be run many times with run_prepared
+        (a stream of batches re-uses its frame descriptors instead of rebuilding them per call)."""
         n = len(frames)
         arr = (abi.vm_frame * max(n, 1))()
         keep = []
@@ -299,10 +301,17 @@ class Engine:
                     keep.append(img)
                     arr[i].image = img.ctypes.data
                 arr[i].format = int(fr.format)
+        return (arr, n, keep)
+
+    def run_prepared(self, prepared, results_on_device=False, time_stages=False, raw=False):
+        arr, n, _ = prepared
         flags = (abi.VM_RESULTS_ON_DEVICE if results_on_device else 0) | (abi.VM_TIME_STAGES if time_stages else 0)
-        raw = abi.vm_batch_result()
-        abi.check(self._lib.vm_run_batch(self._ptr, arr, n, flags, C.byref(raw)))
-        return BatchResult(raw)
+        res = abi.vm_batch_result()
+        abi.check(self._lib.vm_run_batch(self._ptr, arr, n, flags, C.byref(res)))
+        return res if raw else BatchResult(res)
+
+    def run_batch(self, frames: Sequence[FrameInput], results_on_device=False, time_stages=False) -> BatchResult:
+        return self.run_prepared(self.prepare_batch(frames), results_on_device, time_stages)
 
     def __call__(self, mesh, Hoc, lens, image=None, format=None, ranges="host"):
         """The two reference calls. ranges="host" runs Mesh::lookup on the host as the reference engines do
@@ -326,6 +335,16 @@ class Engine:
         ms = (C.c_float * max(n.value, 1))()
         abi.check(self._lib.vm_stage_times(self._ptr, names, ms, n.value, C.byref(n)))
         return [(names[i].decode(), float(ms[i])) for i in range(n.value)]
+
+    def timer_start(self):
+        """Starts the engine's device-side stopwatch (a CUDA event on its own stream)."""
+        abi.check(self._lib.vm_timer_start(self._ptr))
+
+    def timer_stop(self) -> float:
+        """Milliseconds of device time since timer_start, measured after all of the engine's streams."""
+        ms = C.c_float(0)
+        abi.check(self._lib.vm_timer_stop(self._ptr, C.byref(ms)))
+        return float(ms.value)
 
     def launch_count(self) -> int:
         return int(self._lib.vm_launch_count(self._ptr))
