@@ -166,6 +166,37 @@ VM_API vm_status vm_classify(vm_engine* engine,
                       uint32_t format,
                       vm_batch_result* out);
 
+/* No counterpart in the reference.
+ * Projection of one frame (operator()(mesh, Hoc, lens) with the lookup on the device) for callers that must not
+ * allocate device memory while they run: a camera thread inside a fixed-period control loop, where the driver lock and
+ * the implicit device synchronisation of cudaMalloc/cudaFree show up as missed frame deadlines, or a process in which
+ * another framework's caching allocator already owns all of the GPU's memory so that a fresh allocation fails.
+ * Every intermediate of the call (frame constants, BSP element states, per-candidate pixels and node ids, per-block
+ * counts, the node -> point table, the point count) lives in one array that is part of the library image itself,
+ * about 4.3 MB, resident on every GPU that loads the library until the process exits. The call makes no
+ * cudaMalloc/cudaFree and uses no allocating library routine; inputs (a mesh uploaded earlier with its BSP) and
+ * outputs (device buffers of the caller) are passed in.
+ * Limits: mesh->n_nodes <= VM_STATIC_MAX_NODES and its BSP <= VM_STATIC_MAX_BSP elements; larger meshes are
+ * rejected with VM_ERR_INVALID_ARGUMENT and a message naming the limit.
+ * Outputs, all DEVICE pointers sized for the whole mesh: pixel_coordinates n_nodes x 2, global_indices n_nodes,
+ * neighbourhood (n_nodes + 1) x n_neighbours; the first n (+1 for neighbourhood) entries are written. n is stored to
+ * *d_n_points (device, may be NULL) and to *n_points (host, may be NULL). The call returns after its work has finished.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) - make that first call
+ * during set-up, before any stream capture. All calls share the one array and it keeps the previous call's contents
+ * (the cells that must start at zero are cleared by each call): two calls whose GPU work overlaps - from two engines,
+ * threads or processes' streams on the same device within one process - race on it, so serialise them. */
+#define VM_STATIC_MAX_NODES 262144
+#define VM_STATIC_MAX_BSP 131072
+VM_API vm_status vm_project_static(vm_engine* engine,
+                                   const vm_mesh* mesh,
+                                   const float Hoc[16],
+                                   const vm_lens* lens,
+                                   float* d_pixel_coordinates,
+                                   int32_t* d_global_indices,
+                                   int32_t* d_neighbourhood,
+                                   int32_t* d_n_points,
+                                   int32_t* n_points);
+
 /* Stand-alone stages on caller-provided HOST arrays, for testing a stage against the reference function it
  * replaces with identical inputs.
  * vm_sample: cpu::interpolate (cpp/visualmesh/engine/cpu/pixel.hpp:116-144) at n pixel coordinates -> n x 4 floats.

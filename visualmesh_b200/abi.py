@@ -79,6 +79,8 @@ SYMBOLS = {
                              C.POINTER(vm_batch_result)]),
     "vm_classify": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.POINTER(vm_lens), C.c_void_p,
                               C.c_uint32, C.POINTER(vm_batch_result)]),
+    "vm_project_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(vm_lens), C.c_void_p, C.c_void_p,
+                                    C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]),
     "vm_sample": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32, C.c_int32, C.c_uint32, C.c_void_p]),
     "vm_network": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]),
     "vm_stage_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_char_p), C.POINTER(C.c_float), C.c_int32,

@@ -959,6 +959,109 @@ vm_status vm_network(vm_engine* e, const float* input, const int32_t* neighbourh
     return VM_OK;
 }
 
+// ---- projection without any allocation ----------------------------------------------------------------------------
+// All scratch of this entry point is one array inside the library image. In host code `g_static_scratch` is only a
+// stand-in for the symbol; the address the kernels need comes from cudaGetSymbolAddress, looked up once per device.
+namespace {
+constexpr size_t align256(size_t v) {
+    return (v + 255) & ~size_t(255);
+}
+constexpr size_t ST_FRAME   = 0;
+constexpr size_t ST_CELLS   = ST_FRAME + align256(sizeof(vm::FrameParams));  // offsets[2], abort flag
+constexpr size_t ST_BLOCKS  = ST_CELLS + 256;
+constexpr size_t ST_STATE   = ST_BLOCKS + align256(sizeof(int32_t) * (VM_STATIC_MAX_NODES / vm::SELECT_THREADS + 2));
+constexpr size_t ST_CAND_PX = ST_STATE + align256(VM_STATIC_MAX_BSP);
+constexpr size_t ST_CAND_ID = ST_CAND_PX + align256(sizeof(float2) * VM_STATIC_MAX_NODES);
+constexpr size_t ST_RANK    = ST_CAND_ID + align256(sizeof(int32_t) * VM_STATIC_MAX_NODES);
+constexpr size_t ST_BYTES   = ST_RANK + align256(sizeof(int32_t) * VM_STATIC_MAX_NODES);
+
+static __device__ __align__(256) unsigned char g_static_scratch[ST_BYTES];
+
+constexpr int ST_MAX_DEVICES = 64;
+unsigned char* g_static_address[ST_MAX_DEVICES] = {};
+}  // namespace
+
+vm_status vm_project_static(vm_engine* e,
+                            const vm_mesh* mesh,
+                            const float Hoc[16],
+                            const vm_lens* lens,
+                            float* d_px,
+                            int32_t* d_gi,
+                            int32_t* d_nb,
+                            int32_t* d_n_points,
+                            int32_t* n_points) {
+    if (e == nullptr || mesh == nullptr || Hoc == nullptr || lens == nullptr || d_px == nullptr || d_gi == nullptr || d_nb == nullptr) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "null argument");
+    }
+    if (lens->projection != VM_RECTILINEAR && lens->projection != VM_EQUISOLID && lens->projection != VM_EQUIDISTANT) {
+        return fail(VM_ERR_UNSUPPORTED_LENS, "Cannot project: Unknown lens type");
+    }
+    if (mesh->n_bsp == 0) return fail(VM_ERR_NO_BSP, "vm_project_static looks up on the device: the mesh needs vm_mesh_set_bsp");
+    if (mesh->n_nodes > VM_STATIC_MAX_NODES) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "mesh has " + std::to_string(mesh->n_nodes) + " nodes; vm_project_static holds at most VM_STATIC_MAX_NODES = "
+                                               + std::to_string(VM_STATIC_MAX_NODES));
+    }
+    if (mesh->n_bsp > VM_STATIC_MAX_BSP) {
+        return fail(VM_ERR_INVALID_ARGUMENT, "mesh BSP has " + std::to_string(mesh->n_bsp) + " elements; vm_project_static holds at most VM_STATIC_MAX_BSP = "
+                                               + std::to_string(VM_STATIC_MAX_BSP));
+    }
+    if (e->device < 0 || e->device >= ST_MAX_DEVICES) return fail(VM_ERR_INVALID_ARGUMENT, "device ordinal out of range");
+    try {
+        VM_CUDA(cudaSetDevice(e->device));
+        if (g_static_address[e->device] == nullptr) {
+            // once per device, with that device current
+            unsigned char* address = nullptr;
+            VM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch));
+            g_static_address[e->device] = address;
+        }
+        unsigned char* base   = g_static_address[e->device];
+        auto* d_frame         = reinterpret_cast<FrameParams*>(base + ST_FRAME);
+        auto* d_cells         = reinterpret_cast<int32_t*>(base + ST_CELLS);  // [0], [1] offsets, [2] abort
+        auto* d_blocks        = reinterpret_cast<int32_t*>(base + ST_BLOCKS);
+        auto* d_state         = reinterpret_cast<uint8_t*>(base + ST_STATE);
+        auto* d_cand_px       = reinterpret_cast<float2*>(base + ST_CAND_PX);
+        auto* d_cand_node     = reinterpret_cast<int32_t*>(base + ST_CAND_ID);
+        auto* d_rank          = reinterpret_cast<int32_t*>(base + ST_RANK);
+
+        vm_frame fr{};
+        fr.mesh = mesh;
+        std::memcpy(fr.Hoc, Hoc, sizeof(fr.Hoc));
+        fr.lens = *lens;
+        FrameParams p;
+        std::memset(&p, 0, sizeof(p));
+        if (!fill_frame_params(fr, p)) return fail(VM_ERR_UNSUPPORTED_LENS, "Cannot project: Unknown lens type");
+        p.n_candidates = mesh->n_nodes;
+
+        cudaStream_t s = e->lanes[0].stream;
+        VM_CUDA(cudaMemcpyAsync(d_frame, &p, sizeof(p), cudaMemcpyHostToDevice, s));
+        // the array keeps the last call's contents: the running offset and the abort flag must start at zero
+        VM_CUDA(cudaMemsetAsync(d_cells, 0, 4 * sizeof(int32_t), s));
+        const int blocks = (mesh->n_nodes + SELECT_THREADS - 1) / SELECT_THREADS;
+        k_bsp_state<<<dim3((mesh->n_bsp + SELECT_THREADS - 1) / SELECT_THREADS, 1), SELECT_THREADS, 0, s>>>(d_frame, d_state);
+        k_select<<<dim3(blocks, 1), SELECT_THREADS, 0, s>>>(d_frame, d_state, d_cand_px, d_cand_node, d_blocks, d_cells + 2);
+        k_scan<<<1, 1024, 0, s>>>(d_blocks, blocks, blocks, 1, d_cells, 0);
+        k_scatter<<<dim3(blocks, 1), SELECT_THREADS, 0, s>>>(d_frame, d_cand_px, d_cand_node, d_blocks, d_cells, 0,
+                                                             reinterpret_cast<float2*>(d_px), d_gi, d_rank);
+        dim3 g((mesh->n_nodes + 1 + ROW_THREADS - 1) / ROW_THREADS, 1);
+        if (mesh->n_neighbours == 4) k_remap<4><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb);
+        else if (mesh->n_neighbours == 6) k_remap<6><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb);
+        else k_remap<8><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb);
+        VM_CUDA(cudaGetLastError());
+        e->launches += 5;
+        if (d_n_points != nullptr) VM_CUDA(cudaMemcpyAsync(d_n_points, d_cells + 1, sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
+        int32_t cells[3] = {0, 0, 0};
+        VM_CUDA(cudaMemcpyAsync(cells, d_cells, sizeof(cells), cudaMemcpyDeviceToHost, s));
+        VM_CUDA(cudaStreamSynchronize(s));
+        if (cells[2] != 0) return fail(VM_ERR_DEVICE_ABORT, "a kernel gave up on a bounded loop (BSP deeper than 128 levels)");
+        if (n_points != nullptr) *n_points = cells[1];
+    }
+    catch (const CudaFailure& f) {
+        cudaGetLastError();
+        return fail(VM_ERR_CUDA, std::string(cudaGetErrorName(f.code)) + ": " + cudaGetErrorString(f.code) + " in " + f.what);
+    }
+    return VM_OK;
+}
+
 vm_status vm_stage_times(vm_engine* e, const char** names, float* ms, int32_t capacity, int32_t* n) {
     if (e == nullptr || n == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "null argument");
     *n = static_cast<int32_t>(e->stage_ms.size());
