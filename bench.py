@@ -32,6 +32,7 @@ for p in (ROOT, os.path.join(ROOT, "tests")):
 
 import numpy as np  # noqa: E402
 
+from visualmesh_b200 import sharding  # noqa: E402
 from visualmesh_b200 import workloads as W  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture summarised in
@@ -72,20 +73,26 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 6:
-                self.samples.append(parts)
+                self.samples.append((time.time(), parts))
 
-    def stop(self):
+    def stop(self, windows):
+        """windows: [(t0, t1)] host-clock intervals of the timed regions. Samples inside them are "under load"; a
+        region shorter than the sampling period takes the samples closest to it."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.25)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        inside = [p for t, p in self.samples if any(a <= t <= b + 0.12 for a, b in windows)]
+        if not inside and self.samples and windows:
+            mid = 0.5 * (windows[0][0] + windows[-1][1])
+            inside = [p for _, p in sorted(self.samples, key=lambda tp: abs(tp[0] - mid))[:2]]
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        for s in inside:
             try:
                 sm.append(float(s[0]))
                 mx.append(float(s[1]))
@@ -105,11 +112,6 @@ def _physical_device(local_rank):
         if local_rank < len(ids) and ids[local_rank].isdigit():
             return int(ids[local_rank])
     return local_rank
-
-
-def _rank_frames(wl, rank, per_gpu):
-    """Rank r takes frames r*per_gpu .. of the configuration's seeded stream."""
-    return wl.frames[rank * per_gpu:(rank + 1) * per_gpu]
 
 
 # ---------------------------------------------------------------------------------------------------------------------
@@ -209,9 +211,11 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
 
+    sampler = ClockSampler(_physical_device(local_rank))
+    sampler.start()
     per_gpu = args.frames
     wl = W.config(args.config, seed=args.seed, n_frames=per_gpu * world)
-    frames = _rank_frames(wl, rank, per_gpu)
+    frames = sharding.shard(wl.frames, rank, world)  # rank r takes its contiguous slice of the seeded stream
     engine = Engine(wl.network, device=local_rank)
     meshes = {}
     for fr in frames:
@@ -250,13 +254,11 @@ def run_ours(args, rank, world, local_rank):
     warm = max(args.warmup, 3)
     for _ in range(warm):
         engine.run_prepared(dev_batch, results_on_device=True, time_stages=True, raw=True)
-    sampler = ClockSampler(_physical_device(local_rank))
     barrier()
-    sampler.start()
     launches0 = engine.launch_count()
     stage_total, stage_launches = {}, {}
     points = 0
-    t0 = time.perf_counter()
+    t0, w0 = time.perf_counter(), time.time()
     engine.timer_start()
     for _ in range(args.steps):
         res = engine.run_prepared(dev_batch, results_on_device=True, time_stages=True, raw=True)
@@ -265,10 +267,9 @@ def run_ours(args, rank, world, local_rank):
             stage_total[name] = stage_total.get(name, 0.0) + ms
             stage_launches[name] = stage_launches.get(name, 0) + 1
     device_ms = engine.timer_stop()
-    wall = time.perf_counter() - t0
+    wall, w1 = time.perf_counter() - t0, time.time()
     launches = engine.launch_count() - launches0
     barrier()
-    clocks = sampler.stop()
     elapsed = max_over_ranks(device_ms * 1e-3)  # CUDA events on the engine's own stream, max over ranks
     total_frames = per_gpu * world * args.steps
     total_points = sum_over_ranks(points)
@@ -279,7 +280,7 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(warm):
         engine.run_prepared(host_batch, raw=True)
     barrier()
-    t1 = time.perf_counter()
+    t1, w2 = time.perf_counter(), time.time()
     engine.timer_start()
     d2h = 0
     for _ in range(args.steps):
@@ -288,7 +289,8 @@ def run_ours(args, rank, world, local_rank):
         n_rows = n_pts + res.n_frames
         d2h = n_pts * (8 + 4) + n_rows * 4 * res.n_neighbours + n_rows * 4 * res.n_classes + 4 * res.n_frames
     e2e_device_ms = engine.timer_stop()
-    e2e_wall = time.perf_counter() - t1
+    e2e_wall, w3 = time.perf_counter() - t1, time.time()
+    clocks = sampler.stop([(w0, w1), (w2, w3)])
     e2e_elapsed = max_over_ranks(max(e2e_device_ms * 1e-3, e2e_wall))  # the host sees its results inside the region
     barrier()
     e2e_value = total_frames / e2e_elapsed

@@ -181,6 +181,9 @@ VM_API vm_status vm_classify(vm_engine* engine,
  * Outputs, all DEVICE pointers sized for the whole mesh: pixel_coordinates n_nodes x 2, global_indices n_nodes,
  * neighbourhood (n_nodes + 1) x n_neighbours; the first n (+1 for neighbourhood) entries are written. n is stored to
  * *d_n_points (device, may be NULL) and to *n_points (host, may be NULL). The call returns after its work has finished.
+ * The last-bit correction tables of acosf/sinf/tanf (built, with an allocation, by the first vm_run_batch/vm_project/
+ * vm_classify on a device) are used when they already exist and never built here; without them a pixel coordinate can
+ * differ from the reference's in its last bit.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) - make that first call
  * during set-up, before any stream capture. All calls share the one array and it keeps the previous call's contents
  * (the cells that must start at zero are cleared by each call): two calls whose GPU work overlaps - from two engines,

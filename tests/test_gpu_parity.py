@@ -6,9 +6,9 @@ Layers of the check, so that a last-bit difference of a transcendental cannot hi
      (in practice ~1e-6; the only difference is fused multiply-add and the device's expf);
   3. the whole call, host ranges and device lookup, Python front end and the C++ drop-in header.
 On uniform-noise images one ulp of a pixel coordinate already moves a classification by more than 1e-4 through an
-8-layer network, and the host libm's acosf/sinf/tanf are not correctly rounded while the device evaluates them in
-double and rounds once; the end-to-end checks therefore bound the fraction of entries over tolerance instead of
-demanding zero, and print what they saw.
+8-layer network, and the host libm's acosf/sinf/tanf are not correctly rounded. The engine therefore reproduces the
+host libm's last bit from tabulated low bits (csrc/libm_tables.hpp); with that the pixel coordinates are expected to be
+bit-identical and every check below demands the stated tolerances on every entry.
 """
 import numpy as np
 import pytest
@@ -47,8 +47,7 @@ def test_golden_whole_call(cases, name, lookup):
         print(f"{name}[{f}] {lookup}: {rep}")
         assert rep.projection_ok, str(rep)
         assert rep.n_out == rep.n_ref or rep.border_nodes
-        assert rep.max_cls < 5e-3, str(rep)
-        assert rep.cls_over_tol <= max(2, rep.cls_entries // 200), str(rep)
+        assert rep.ok, str(rep)
     engine.close()
 
 
@@ -197,8 +196,8 @@ def _check_config(cfg, n_frames, via_cpp):
         print(f"cfg{cfg}[{f}] {'c++ drop-in' if via_cpp else 'python/C-ABI'}: {rep}")
         assert rep.projection_ok, str(rep)
         assert rep.n_ref > 0
-        assert rep.max_cls < 2e-2, str(rep)
-        assert rep.cls_over_tol <= max(2, rep.cls_entries // 200), str(rep)
+        assert rep.ok, str(rep)
+        assert rep.px_bit_identical > 0.999, str(rep)
         frames_ok += rep.ok
     engine.close()
     return frames_ok
@@ -237,6 +236,5 @@ def test_config3_dense_mesh_projection_and_two_layers():
     out = engine.run_batch([FrameInput(Mesh.from_spec(fr.mesh), fr.Hoc, fr.lens, image, fr.format, None)]).frame(0)
     rep = P.compare(out, ref, fr.lens.dimensions)
     print(f"cfg3 (2 layers): {rep}")
-    assert rep.projection_ok and rep.n_ref > 900000, str(rep)
-    assert rep.cls_over_tol <= rep.cls_entries // 200, str(rep)
+    assert rep.ok and rep.n_ref > 900000, str(rep)
     engine.close()

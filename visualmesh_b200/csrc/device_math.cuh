@@ -41,6 +41,10 @@ struct FrameParams {
     int32_t node_off;     // first entry of this frame's node -> local index table inside the chunk
     int32_t bsp_off;      // first entry of this frame's BSP state table inside the chunk
     int32_t image_row_bytes;
+    // low two bits of the host libm's acosf / sinf / tanf per input float (libm_tables.hpp); nullptr = not tabulated
+    const uint32_t* libm_acos;
+    const uint32_t* libm_sin;
+    const uint32_t* libm_tan;
 };
 
 __device__ __forceinline__ float dot3(float a0, float a1, float a2, float b0, float b1, float b2) {
@@ -48,16 +52,27 @@ __device__ __forceinline__ float dot3(float a0, float a1, float a2, float b0, fl
     return __fadd_rn(__fmul_rn(a2, b2), __fadd_rn(__fmul_rn(a1, b1), __fmul_rn(a0, b0)));
 }
 
-// The host libm's acosf/sinf/tanf are within 1 ulp of the correctly rounded result; evaluating in double and rounding
-// once gives the correctly rounded float, the closest principled target.
-__device__ __forceinline__ float acos_rn(float x) {
-    return __double2float_rn(acos(static_cast<double>(x)));
+// The host libm's acosf/sinf/tanf are within 1 ulp of the exact result; evaluating in double and rounding once gives
+// the correctly rounded float, which is within one ulp of the host's. `as_host_libm` then moves it by at most one
+// ulp onto the host libm's own result, using the tabulated low two bits of that result (libm_tables.hpp).
+__device__ __forceinline__ float as_host_libm(float approx, float x, const uint32_t* table, uint32_t first_bits, uint32_t end_bits) {
+    const uint32_t bx = __float_as_uint(x);
+    if (table == nullptr || bx < first_bits || bx >= end_bits) return approx;
+    const uint32_t i    = bx - first_bits;
+    const uint32_t code = (__ldg(table + (i >> 4)) >> ((i & 15u) * 2u)) & 3u;
+    uint32_t ba         = __float_as_uint(approx);
+    const uint32_t d    = (code - (ba & 3u)) & 3u;  // 0: same, 1: one ulp up, 3: one ulp down
+    ba += (d == 1u) ? 1u : (d == 3u) ? 0xFFFFFFFFu : 0u;
+    return __uint_as_float(ba);
 }
-__device__ __forceinline__ float sin_rn(float x) {
-    return __double2float_rn(sin(static_cast<double>(x)));
+__device__ __forceinline__ float acos_rn(float x, const uint32_t* table) {
+    return as_host_libm(__double2float_rn(acos(static_cast<double>(x))), x, table, 0x3A800000u, 0x3F800000u);
 }
-__device__ __forceinline__ float tan_rn(float x) {
-    return __double2float_rn(tan(static_cast<double>(x)));
+__device__ __forceinline__ float sin_rn(float x, const uint32_t* table) {
+    return as_host_libm(__double2float_rn(sin(static_cast<double>(x))), x, table, 0x3A800000u, 0x3F800000u);
+}
+__device__ __forceinline__ float tan_rn(float x, const uint32_t* table) {
+    return as_host_libm(__double2float_rn(tan(static_cast<double>(x))), x, table, 0x3A800000u, 0x40000000u);
 }
 
 // cpp/visualmesh/utility/projection.hpp:105-120: float products, double running sum, one rounding at the end
@@ -78,7 +93,7 @@ __device__ __forceinline__ float distort(float r, const float* ik) {
 // cpp/visualmesh/utility/projection.hpp:163-187 on a camera-space unit vector
 __device__ __forceinline__ float2 project(float rx, float ry, float rz, const FrameParams& p) {
     const float f          = p.focal_length;
-    const float theta      = acos_rn(rx);
+    const float theta      = acos_rn(rx, p.libm_acos);
     const float rsin_theta = __fdiv_rn(1.0f, __fsqrt_rn(__fsub_rn(1.0f, __fmul_rn(rx, rx))));
     float r_u;
     if (p.projection == VM_RECTILINEAR) {
@@ -86,10 +101,10 @@ __device__ __forceinline__ float2 project(float rx, float ry, float rz, const Fr
         const float pi_2 = 1.57079637050628662109375f;
         float t          = (theta < 0.0f) ? 0.0f : theta;
         t                = (pi_2 < t) ? pi_2 : t;
-        r_u              = __fmul_rn(f, tan_rn(t));
+        r_u              = __fmul_rn(f, tan_rn(t, p.libm_tan));
     }
     else if (p.projection == VM_EQUISOLID) {
-        r_u = __fmul_rn(__fmul_rn(2.0f, f), sin_rn(__fmul_rn(theta, 0.5f)));
+        r_u = __fmul_rn(__fmul_rn(2.0f, f), sin_rn(__fmul_rn(theta, 0.5f), p.libm_sin));
     }
     else {
         r_u = __fmul_rn(f, theta);

@@ -11,12 +11,14 @@
 #include <cstdlib>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
 #include "../../include/vmcuda.h"
 #include "host_math.hpp"
 #include "kernels.cuh"
+#include "libm_tables.hpp"
 
 namespace vm {
 
@@ -79,6 +81,28 @@ struct PinnedArray {
         cap = 0;
     }
 };
+
+// Device copies of the libm last-bit tables, built on first use and shared by all engines of a process (per device).
+constexpr int LIBM_MAX_DEVICES = 64;
+static uint32_t* g_libm_device[LIBM_MAX_DEVICES][libm::N_FUNCTIONS] = {};
+static std::mutex g_libm_mutex;
+
+static const uint32_t* libm_table(int device, int fn, bool build_if_missing) {
+    static const bool disabled = [] {
+        const char* v = std::getenv("VMCUDA_LIBM_TABLES");
+        return v != nullptr && v[0] == '0';
+    }();
+    if (disabled || device < 0 || device >= LIBM_MAX_DEVICES) return nullptr;
+    std::lock_guard<std::mutex> lock(g_libm_mutex);
+    if (g_libm_device[device][fn] == nullptr && build_if_missing) {
+        const std::vector<uint32_t> packed = libm::build(fn);
+        uint32_t* d = nullptr;
+        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&d), packed.size() * sizeof(uint32_t)));
+        VM_CUDA(cudaMemcpy(d, packed.data(), packed.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+        g_libm_device[device][fn] = d;
+    }
+    return g_libm_device[device][fn];
+}
 
 struct DenseLayer {
     float* d_weights = nullptr;  // [n_slots * cin][coutp] then [coutp] biases
@@ -256,7 +280,7 @@ static void run_network(vm_engine* e,
 
 // ---- per-frame constants -----------------------------------------------------------------------------------------
 
-static bool fill_frame_params(const vm_frame& fr, FrameParams& p) {
+static bool fill_frame_params(const vm_frame& fr, FrameParams& p, int device, bool may_allocate = true) {
     const float* H = fr.Hoc;
     // Rco = block<3,3>(transpose(Hoc)), cpp/visualmesh/engine/cpu/engine.hpp:95
     for (int i = 0; i < 3; ++i)
@@ -285,6 +309,9 @@ static bool fill_frame_params(const vm_frame& fr, FrameParams& p) {
             p.edges[i][4] = edges[i].sin_t;
         }
     }
+    p.libm_acos = libm_table(device, libm::ACOS, may_allocate);
+    p.libm_sin  = fr.lens.projection == VM_EQUISOLID ? libm_table(device, libm::SIN, may_allocate) : nullptr;
+    p.libm_tan  = fr.lens.projection == VM_RECTILINEAR ? libm_table(device, libm::TAN, may_allocate) : nullptr;
     const vm_mesh* m = fr.mesh;
     p.rays           = m->d_rays;
     p.neighbours     = m->d_neighbours;
@@ -332,7 +359,7 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
         const vm_frame& fr = frames[f];
         FrameParams& p     = lane.h_frames.p[f - f0];
         std::memset(&p, 0, sizeof(p));
-        fill_frame_params(fr, p);
+        fill_frame_params(fr, p, e->device);
         const int64_t nc = frame_candidates(fr);
         p.n_candidates   = static_cast<int32_t>(nc);
         p.cand_off       = static_cast<int32_t>(cand_total);
@@ -1029,7 +1056,8 @@ vm_status vm_project_static(vm_engine* e,
         fr.lens = *lens;
         FrameParams p;
         std::memset(&p, 0, sizeof(p));
-        if (!fill_frame_params(fr, p)) return fail(VM_ERR_UNSUPPORTED_LENS, "Cannot project: Unknown lens type");
+        // never builds the libm last-bit tables here (that allocates): they are used only if an earlier call built them
+        if (!fill_frame_params(fr, p, e->device, false)) return fail(VM_ERR_UNSUPPORTED_LENS, "Cannot project: Unknown lens type");
         p.n_candidates = mesh->n_nodes;
 
         cudaStream_t s = e->lanes[0].stream;
