@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libvmcuda.so")
 SOURCES = ["engine.cu", "hostmesh.cpp"]
-HEADERS = ["kernels.cuh", "device_math.cuh", "host_math.hpp", "libm_tables.hpp", os.path.join("..", "..", "include", "vmcuda.h")]
+HEADERS = ["kernels.cuh", "conv_tc.cuh", "device_math.cuh", "host_math.hpp", "libm_tables.hpp", os.path.join("..", "..", "include", "vmcuda.h")]
 
 
 def _nvcc():

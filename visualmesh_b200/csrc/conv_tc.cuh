@@ -1,0 +1,382 @@
+// Graph-convolution layer on the 5th-generation tensor cores (tcgen05) with fp32-grade accuracy.
+//
+// out[row] = act(bias + sum_s  X[nbr_s(row)] . W_s)  is a [rows x K] x [K x COUT] product whose A operand is a GATHER:
+// K = (N+1) * CIN, slot s of row r is the feature row of r's s-th neighbour. A CTA owns 128-row tiles. For every slot
+// its 128 threads (thread = row) read the neighbour's feature chunks (coalesced in the chunk-planar layout), split
+// each fp32 value x into two parts x = hi + lo (two fp16 values, or a TF32 and its remainder for 8-channel layers) and
+// store both into shared memory in the canonical K-major no-swizzle UMMA layout; one thread then issues
+//     D[:, 0:2NP] += A_hi . [B_hi | B_lo]      D[:, 0:NP] += A_lo . B_hi        (tcgen05.mma, M = 128)
+// against the layer's weights, which sit in shared memory pre-split the same way; the epilogue adds the two halves
+// of D. Dropping only lo*lo keeps the product within ~2^-21 relative of fp32, far inside the 1e-4 tolerance that
+// rules out a single reduced-precision pass.
+// The accumulator lives in tensor memory (two buffers, so a tile's epilogue never meets the next tile's first MMA);
+// the epilogue reads it with tcgen05.ld (thread = row again), adds the bias, applies the activation and writes the
+// output row. Shared-memory stages are recycled through mbarriers armed by tcgen05.commit.
+//
+// Every wait is bounded: a wait that runs out raises the abort flag, the CTA stops issuing work, frees its tensor
+// memory and returns, and the host reports VM_ERR_DEVICE_ABORT.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "kernels.cuh"
+
+namespace vm {
+namespace tc {
+
+    constexpr int TILE_ROWS     = 128;
+    constexpr int THREADS       = 128;
+    constexpr int MAX_FRAMES    = 64;       // frames per launch whose tile counts fit the shared prefix table
+    constexpr uint32_t WAIT_LIMIT = 4000000;  // polls of mbarrier.try_wait before giving up
+    constexpr int ABORT_TC_TIMEOUT = 2;
+
+    __device__ __forceinline__ uint32_t smem_u32(const void* p) {
+        return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+    }
+    __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+    }
+    __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+        uint32_t ok;
+        asm volatile(
+          "{\n\t"
+          ".reg .pred p;\n\t"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t"
+          "}\n"
+          : "=r"(ok)
+          : "r"(bar), "r"(parity)
+          : "memory");
+        return ok != 0;
+    }
+    // false when the limit ran out
+    __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+        for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+        }
+        return false;
+    }
+
+    // K-major, no swizzle: 8-row x 16-byte core matrices; LBO = distance between the two 16-byte K chunks of one MMA,
+    // SBO = distance between 8-row groups. Version 1 = Blackwell descriptor.
+    __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+        return static_cast<uint64_t>((addr >> 4) & 0x3FFFu) | (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16)
+               | (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46);
+    }
+
+    __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+        asm volatile(
+          "{\n\t"
+          ".reg .pred p;\n\t"
+          "setp.ne.b32 p, %4, 0;\n\t"
+          "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+          "}\n" ::"r"(tmem_d),
+          "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+          : "memory");
+    }
+    __device__ __forceinline__ void commit(uint32_t bar) {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    }
+
+    struct Args {
+        const void* w_cat;  // [K / KCH chunks][2 * NP rows][16 bytes]: rows 0..NP-1 = hi parts, NP..2NP-1 = lo parts
+        const float* bias;  // [NP]
+        int32_t n_frames;
+        int32_t cout;
+        int32_t* abort_flag;
+    };
+
+    constexpr int ABORT_TC_RANGE = 3;  // a feature value too large for the fp16 split: the host falls back to FFMA
+
+    // Element formats of the split. HALF: x = h + l with h, l fp16 (kind::f16, 8 channels per 16-byte chunk, K = 16
+    // per MMA) - half the shared-memory traffic of the fp32 container formats, needs |x| < 65504. Otherwise TF32:
+    // h = x with 13 mantissa bits cleared, l = x - h (kind::tf32, 4 channels per chunk, K = 8 per MMA).
+    template <bool HALF>
+    struct Format {
+        static constexpr int KCH          = HALF ? 8 : 4;  // channels per 16-byte chunk
+        static constexpr uint32_t AB_CODE = HALF ? 0u : 2u;  // instruction-descriptor format code of A and B
+    };
+
+    template <bool HALF>
+    __device__ __forceinline__ void mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+        if (HALF) {
+            asm volatile(
+              "{\n\t"
+              ".reg .pred p;\n\t"
+              "setp.ne.b32 p, %4, 0;\n\t"
+              "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+              "}\n" ::"r"(tmem_d),
+              "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+              : "memory");
+        }
+        else {
+            mma_tf32(tmem_d, desc_a, desc_b, idesc, accumulate);
+        }
+    }
+
+    // shared memory: [stages][hi, lo][planes][128 rows][16 B], then the concatenated weights
+    template <int CIN, int NP, int STAGES, bool HALF>
+    constexpr size_t smem_bytes(int n_slots) {
+        return 256 + static_cast<size_t>(STAGES) * 2 * (CIN / Format<HALF>::KCH) * TILE_ROWS * 16
+               + static_cast<size_t>(n_slots) * (CIN / Format<HALF>::KCH) * 2 * NP * 16;
+    }
+
+    // The two products of one K step:  D[:, 0:2NP] += A_hi . [B_hi | B_lo]   and   D[:, 0:NP] += A_lo . B_hi ;
+    // the epilogue adds the two halves of D. A is read twice per K step instead of three times.
+    template <int CIN, int NP, int STAGES, int NSLOTS, bool HALF>
+    __global__ void __launch_bounds__(THREADS) k_graph_conv_tc(const ConvArgs a, const Args t) {
+        static_assert(NP == 16 || NP == 32, "unsupported tile width");
+        constexpr int KCH        = Format<HALF>::KCH;
+        static_assert(CIN % (2 * KCH) == 0, "a slot must hold whole K steps");
+        constexpr int PLANES     = CIN / KCH;            // 16-byte chunks per row and slot
+        constexpr int PLANE      = TILE_ROWS * 16;       // bytes of one chunk over the 128 rows
+        constexpr int SLOT_BYTES = PLANES * PLANE;       // one slot, hi or lo
+        constexpr int WCHUNK     = 2 * NP * 16;          // bytes of one weight chunk: hi rows then lo rows
+        constexpr int TMEM_COLS  = 4 * NP;               // two accumulator buffers of 2 * NP columns
+
+        extern __shared__ __align__(1024) unsigned char smem_raw[];
+        __shared__ uint64_t bars[STAGES + 2];
+        __shared__ uint32_t tmem_base_slot;
+        __shared__ int32_t tile_prefix[MAX_FRAMES + 1];
+        __shared__ int32_t failed;
+
+        const int tid  = threadIdx.x;
+        const int warp = tid >> 5;
+        unsigned char* stage_base = smem_raw;
+        unsigned char* w_s        = smem_raw + static_cast<size_t>(STAGES) * 2 * SLOT_BYTES;
+
+        // ---- set-up ----
+        if (tid == 0) {
+            failed = 0;
+            for (int i = 0; i < STAGES + 2; ++i) mbar_init(smem_u32(&bars[i]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            int run = 0;
+            for (int f = 0; f < t.n_frames; ++f) {
+                tile_prefix[f] = run;
+                const int rows = a.offsets[a.f0 + f + 1] - a.offsets[a.f0 + f] + 1;
+                run += (rows + TILE_ROWS - 1) / TILE_ROWS;
+            }
+            tile_prefix[t.n_frames] = run;
+        }
+        if (warp == 0) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        {
+            const uint4* g = reinterpret_cast<const uint4*>(t.w_cat);
+            uint4* sw      = reinterpret_cast<uint4*>(w_s);
+            for (int i = tid; i < NSLOTS * PLANES * 2 * NP; i += THREADS) sw[i] = __ldg(g + i);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_base = tmem_base_slot;
+        const int total_tiles    = tile_prefix[t.n_frames];
+
+        // instruction descriptors: D = F32, A and B K-major, M = 128, N = 2 NP (hi | lo weights) or NP (hi weights)
+        constexpr uint32_t IDESC_BASE = (1u << 4) | (Format<HALF>::AB_CODE << 7) | (Format<HALF>::AB_CODE << 10) | (static_cast<uint32_t>(TILE_ROWS >> 4) << 24);
+        constexpr uint32_t IDESC_CAT  = IDESC_BASE | (static_cast<uint32_t>((2 * NP) >> 3) << 17);
+        constexpr uint32_t IDESC_HI   = IDESC_BASE | (static_cast<uint32_t>(NP >> 3) << 17);
+        const uint32_t w_addr = smem_u32(w_s);
+        const float4* in4     = reinterpret_cast<const float4*>(a.in);
+
+        uint32_t it         = 0;  // stage uses so far
+        uint32_t tile_count = 0;
+        bool ok             = true;
+        bool out_of_range   = false;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
+            int f = 0;
+            while (f + 1 < t.n_frames && tile_prefix[f + 1] <= tile) ++f;
+            const int frame      = a.f0 + f;
+            const int start      = a.offsets[frame];
+            const int rows       = a.offsets[frame + 1] - start + 1;
+            const int row        = (tile - tile_prefix[f]) * TILE_ROWS + tid;
+            const int rowc       = min(row, rows - 1);
+            const int local_base = start - a.offsets[a.f0] + f;
+            const size_t nb_base = static_cast<size_t>(start + frame);
+            const uint32_t acc   = tmem_base + (tile_count & 1u) * (2 * NP);
+
+            // all neighbour indices of this row up front, and the first slot's feature chunks: the loads of slot s + 1
+            // are in flight while slot s is split, stored and multiplied
+            int src_rows[NSLOTS];
+            src_rows[0] = local_base + rowc;
+#pragma unroll
+            for (int s = 1; s < NSLOTS; ++s) src_rows[s] = local_base + __ldg(a.nb + (nb_base + rowc) * a.n_neighbours + (s - 1));
+            constexpr int DEPTH = 1;  // slots whose loads are in flight ahead of the one being stored
+            float4 ring[DEPTH][CIN / 4];
+#pragma unroll
+            for (int d = 0; d < DEPTH; ++d) {
+                if (d < NSLOTS) {
+#pragma unroll
+                    for (int c = 0; c < CIN / 4; ++c) ring[d][c] = in4[static_cast<size_t>(c) * a.in_stride + src_rows[d]];
+                }
+            }
+
+#pragma unroll
+            for (int s = 0; s < NSLOTS; ++s, ++it) {
+                const uint32_t stage = it % STAGES;
+                const uint32_t use   = it / STAGES;
+                float4 cur[CIN / 4];
+#pragma unroll
+                for (int c = 0; c < CIN / 4; ++c) cur[c] = ring[s % DEPTH][c];
+                if (s + DEPTH < NSLOTS) {
+#pragma unroll
+                    for (int c = 0; c < CIN / 4; ++c) ring[s % DEPTH][c] = in4[static_cast<size_t>(c) * a.in_stride + src_rows[s + DEPTH]];
+                }
+                if (use > 0 && !mbar_wait(smem_u32(&bars[stage]), (use - 1) & 1u)) { atomicExch(&failed, 1); }
+                unsigned char* hi_p = stage_base + static_cast<size_t>(stage) * 2 * SLOT_BYTES;
+                unsigned char* lo_p = hi_p + SLOT_BYTES;
+                if (HALF) {
+#pragma unroll
+                    for (int p = 0; p < PLANES; ++p) {
+                        const float x[8] = {cur[2 * p].x, cur[2 * p].y, cur[2 * p].z, cur[2 * p].w,
+                                            cur[2 * p + 1].x, cur[2 * p + 1].y, cur[2 * p + 1].z, cur[2 * p + 1].w};
+                        uint32_t h[4], l[4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            out_of_range |= fabsf(x[2 * q]) > 60000.0f || fabsf(x[2 * q + 1]) > 60000.0f;
+                            const __half h0 = __float2half_rn(x[2 * q]);
+                            const __half h1 = __float2half_rn(x[2 * q + 1]);
+                            const __half l0 = __float2half_rn(x[2 * q] - __half2float(h0));
+                            const __half l1 = __float2half_rn(x[2 * q + 1] - __half2float(h1));
+                            h[q] = static_cast<uint32_t>(__half_as_ushort(h0)) | (static_cast<uint32_t>(__half_as_ushort(h1)) << 16);
+                            l[q] = static_cast<uint32_t>(__half_as_ushort(l0)) | (static_cast<uint32_t>(__half_as_ushort(l1)) << 16);
+                        }
+                        *reinterpret_cast<uint4*>(hi_p + p * PLANE + tid * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<uint4*>(lo_p + p * PLANE + tid * 16) = make_uint4(l[0], l[1], l[2], l[3]);
+                    }
+                }
+                else {
+#pragma unroll
+                    for (int c = 0; c < CIN / 4; ++c) {
+                        const float4 x = cur[c];
+                        float4 h, l;
+                        h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+                        h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+                        h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+                        h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+                        l.x = x.x - h.x;
+                        l.y = x.y - h.y;
+                        l.z = x.z - h.z;
+                        l.w = x.w - h.w;
+                        *reinterpret_cast<float4*>(hi_p + c * PLANE + tid * 16) = h;
+                        *reinterpret_cast<float4*>(lo_p + c * PLANE + tid * 16) = l;
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncthreads();
+                if (failed) {
+                    ok = false;
+                    break;
+                }
+                if (tid == 0) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_hi = smem_u32(hi_p);
+                    const uint32_t a_lo = smem_u32(lo_p);
+#pragma unroll
+                    for (int ks = 0; ks < PLANES / 2; ++ks) {
+                        const uint64_t da_hi = smem_desc(a_hi + ks * 2 * PLANE, PLANE, 128);
+                        const uint64_t da_lo = smem_desc(a_lo + ks * 2 * PLANE, PLANE, 128);
+                        const uint64_t db    = smem_desc(w_addr + (s * PLANES + ks * 2) * WCHUNK, WCHUNK, 128);
+                        mma<HALF>(acc, da_hi, db, IDESC_CAT, (s == 0 && ks == 0) ? 0u : 1u);
+                        mma<HALF>(acc, da_lo, db, IDESC_HI, 1u);
+                    }
+                    commit(smem_u32(&bars[stage]));
+                    if (s == NSLOTS - 1) commit(smem_u32(&bars[STAGES + (tile_count & 1u)]));
+                }
+            }
+            if (!ok) break;
+
+            // ---- epilogue: accumulator -> registers -> bias, activation -> global ----
+            // the decision to go on must be the same in every thread: the tensor-memory load below is warp-collective
+            const bool arrived = mbar_wait(smem_u32(&bars[STAGES + (tile_count & 1u)]), (tile_count >> 1) & 1u);
+            ok                 = __syncthreads_and(arrived ? 1 : 0) != 0;
+            if (!ok && tid == 0) failed = 1;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float v[NP];
+            if (ok) {
+#pragma unroll
+                for (int j0 = 0; j0 < 2 * NP; j0 += 16) {
+                    uint32_t r[16];
+                    const uint32_t taddr = acc + (static_cast<uint32_t>(warp * 32) << 16) + j0;
+                    asm volatile(
+                      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                      : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        // columns NP..2NP-1 hold A_hi . B_lo of output column j0 + j - NP
+                        if (j0 < NP) { v[j0 + j] = __uint_as_float(r[j]); }
+                        else {
+                            v[j0 + j - NP] = v[j0 + j - NP] + __uint_as_float(r[j]);
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < NP; ++j) v[j] = v[j] + __ldg(t.bias + j);
+                if (row < rows) {
+                    const size_t out_row = (a.out_global ? nb_base : static_cast<size_t>(local_base)) + row;
+                    if (a.activation == VM_SOFTMAX) {
+                        float total = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            if (j < t.cout) {
+                                v[j]  = expf(v[j]);
+                                total = __fadd_rn(total, v[j]);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) v[j] = __fdiv_rn(v[j], total);
+                    }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            v[j] = a.activation == VM_SELU ? selu(v[j])
+                                   : a.activation == VM_RELU ? ((v[j] < 0.0f) ? 0.0f : v[j])
+                                                             : tanhf(v[j]);
+                        }
+                    }
+                    if (a.out_planar) {
+                        float4* out4 = reinterpret_cast<float4*>(a.out);
+#pragma unroll
+                        for (int j4 = 0; j4 < NP / 4; ++j4) {
+                            if (j4 * 4 < t.cout) {
+                                out4[static_cast<size_t>(j4) * a.out_stride + out_row] = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+                            }
+                        }
+                    }
+                    else {
+                        float* dst = a.out + out_row * t.cout;
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            if (j < t.cout) dst[j] = v[j];
+                        }
+                    }
+                }
+            }
+        }
+
+        // ---- tear-down: nothing of this CTA may still be running on the tensor core when its memory goes away ----
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        const int any_range = __syncthreads_or(out_of_range ? 1 : 0);
+        if (tid == 0) {
+            if (failed) { atomicExch(t.abort_flag, ABORT_TC_TIMEOUT); }
+            else if (any_range) {
+                atomicCAS(t.abort_flag, 0, ABORT_TC_RANGE);
+            }
+        }
+        if (warp == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        }
+    }
+
+}  // namespace tc
+}  // namespace vm

@@ -4,9 +4,11 @@
 // reference engines it is not thread-safe - use one instance per host thread. A batch is cut into chunks of frames;
 // chunks rotate over a few lanes (stream + scratch) so that the host-to-device copy of one chunk's images, the
 // kernels of another and the device-to-host copy of a third overlap.
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -18,6 +20,7 @@
 #include "../../include/vmcuda.h"
 #include "host_math.hpp"
 #include "kernels.cuh"
+#include "conv_tc.cuh"
 #include "libm_tables.hpp"
 
 namespace vm {
@@ -108,6 +111,11 @@ struct DenseLayer {
     float* d_weights = nullptr;  // [n_slots * cin][coutp] then [coutp] biases
     int cin = 0, cout = 0, coutp = 0, n_slots = 1, activation = 0;
     std::string stage;  // name under which this layer's kernel is timed, e.g. "graph_conv_16x16"
+    // tensor-core path (conv_tc.cuh): weights split into TF32 hi/lo parts in the UMMA K-major layout, padded bias
+    void* d_tc_cat   = nullptr;  // [K / KCH chunks][2 * NP rows][16 B]: hi rows then lo rows
+    float* d_tc_bias = nullptr;
+    int tc_np        = 0;      // padded output width of the tensor-core tile, 0 = no tensor-core path for this shape
+    bool tc_half     = false;  // fp16 hi/lo split (16- and 32-channel inputs) or TF32 split (8-channel inputs)
 };
 
 constexpr int MAX_LANES = 3;
@@ -179,6 +187,7 @@ struct vm_engine {
     bool timing        = false;
     std::vector<std::pair<const char*, float>> stage_ms;
     int64_t launches = 0;
+    bool use_tc      = false;
     cudaEvent_t ev_timer_start = nullptr, ev_timer_stop = nullptr;
 };
 
@@ -204,23 +213,39 @@ static void end_stage(vm_engine* e, cudaStream_t s) {
 
 // ---- graph convolution dispatch ----------------------------------------------------------------------------------
 
-template <int CIN, int COUT, int R>
+template <int CIN, int COUT, int R, int T = CONV_THREADS, int MINB = 1>
 static void launch_conv_t(const ConvArgs& a, dim3 grid_rows, int max_rows, cudaStream_t s) {
     constexpr int COUTP = (COUT + 3) & ~3;
     const size_t smem   = (static_cast<size_t>(a.n_slots) * CIN * COUTP + COUTP) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        VM_CUDA(cudaFuncSetAttribute(k_graph_conv<CIN, COUT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        VM_CUDA(cudaFuncSetAttribute(k_graph_conv<CIN, COUT, R, T, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
         configured = true;
     }
-    dim3 grid((max_rows + CONV_THREADS * R - 1) / (CONV_THREADS * R), grid_rows.y);
-    k_graph_conv<CIN, COUT, R><<<grid, CONV_THREADS, smem, s>>>(a);
+    dim3 grid((max_rows + T * R - 1) / (T * R), grid_rows.y);
+    k_graph_conv<CIN, COUT, R, T, MINB><<<grid, T, smem, s>>>(a);
 }
 
 // Shapes with a specialised kernel; anything else takes the generic one.
 static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, int max_rows, cudaStream_t s) {
     const size_t smem = (static_cast<size_t>(a.n_slots) * L.cin * L.coutp + L.coutp) * sizeof(float);
     if (smem > 96 * 1024) return false;
+    static const int variant = [] {
+        const char* v = std::getenv("VMCUDA_CONV_VARIANT");
+        return v != nullptr ? std::atoi(v) : 0;
+    }();
+    if (L.cin == 16 && L.cout == 16 && variant != 0) {
+        switch (variant) {
+            case 1: launch_conv_t<16, 16, 2, 128, 1>(a, grid, max_rows, s); return true;
+            case 2: launch_conv_t<16, 16, 2, 256, 1>(a, grid, max_rows, s); return true;
+            case 3: launch_conv_t<16, 16, 4, 256, 1>(a, grid, max_rows, s); return true;
+            case 4: launch_conv_t<16, 16, 4, 128, 4>(a, grid, max_rows, s); return true;
+            case 5: launch_conv_t<16, 16, 1, 256, 1>(a, grid, max_rows, s); return true;
+            case 6: launch_conv_t<16, 16, 2, 128, 6>(a, grid, max_rows, s); return true;
+            case 7: launch_conv_t<16, 16, 8, 64, 1>(a, grid, max_rows, s); return true;
+            default: break;
+        }
+    }
 #define VM_CONV(CI, CO, RR)                                   \
     if (L.cin == CI && L.cout == CO) {                        \
         launch_conv_t<CI, CO, RR>(a, grid, max_rows, s);      \
@@ -236,6 +261,49 @@ static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, 
     return false;
 }
 
+template <int CIN, int NP, int NSLOTS, bool HALF>
+static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
+    constexpr int STAGES = NSLOTS * CIN <= 160 ? NSLOTS : 3;
+    const size_t smem    = tc::smem_bytes<CIN, NP, STAGES, HALF>(NSLOTS);
+    static int ctas_per_sm = 0;
+    static int n_sms       = 0;
+    if (ctas_per_sm == 0) {
+        VM_CUDA(cudaFuncSetAttribute(tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        int dev = 0;
+        VM_CUDA(cudaGetDevice(&dev));
+        VM_CUDA(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
+        // resident CTAs per SM: shared memory (about 220 KB usable, some per CTA reserved) and tensor memory (512 columns)
+        const int by_smem = static_cast<int>((220 * 1024) / (smem + 2048));
+        const int by_tmem = 512 / (4 * NP);
+        ctas_per_sm       = std::max(1, std::min(std::min(by_smem, by_tmem), 6));
+    }
+    tc::Args t{};
+    t.w_cat      = L.d_tc_cat;
+    t.bias       = L.d_tc_bias;
+    t.n_frames   = n_frames;
+    t.cout       = L.cout;
+    t.abort_flag = abort_flag;
+    const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
+    const int grid        = std::max(1, std::min(tiles_upper, n_sms * ctas_per_sm));
+    tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF><<<grid, tc::THREADS, smem, s>>>(a, t);
+}
+
+static bool launch_conv_tc(vm_engine* e, const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, cudaStream_t s) {
+    if (L.tc_np == 0 || n_frames > tc::MAX_FRAMES) return false;
+#define VM_TC(CI, NPAD, NS, HF)                                                      \
+    if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS && L.tc_half == HF) {        \
+        launch_conv_tc_t<CI, NPAD, NS, HF>(L, a, n_frames, max_rows, e->d_abort, s);   \
+        return true;                                                                  \
+    }
+    VM_TC(8, 16, 5, false) VM_TC(8, 16, 7, false) VM_TC(8, 16, 9, false)
+    VM_TC(16, 16, 5, true) VM_TC(16, 16, 7, true) VM_TC(16, 16, 9, true)
+    VM_TC(16, 32, 7, true) VM_TC(16, 32, 9, true)
+    VM_TC(32, 16, 7, true) VM_TC(32, 16, 9, true)
+    VM_TC(32, 32, 7, true) VM_TC(32, 32, 9, true)
+#undef VM_TC
+    return false;
+}
+
 static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_frames, int max_rows, cudaStream_t s) {
     a.weights     = L.d_weights;
     a.biases      = L.d_weights + static_cast<size_t>(L.n_slots) * L.cin * L.coutp;
@@ -243,7 +311,8 @@ static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_fra
     a.activation  = L.activation;
     dim3 grid(1, n_frames);
     begin_stage(e, s, L.stage.c_str());
-    if (!launch_conv_fast(L, a, grid, max_rows, s)) {
+    if (e->use_tc && launch_conv_tc(e, L, a, n_frames, max_rows, s)) {}
+    else if (!launch_conv_fast(L, a, grid, max_rows, s)) {
         dim3 g((max_rows + CONV_THREADS - 1) / CONV_THREADS, n_frames);
         k_graph_conv_generic<<<g, CONV_THREADS, 0, s>>>(a, L.cin, L.cout, L.coutp);
     }
@@ -261,7 +330,8 @@ static void run_network(vm_engine* e,
                         int n_frames,
                         int max_rows,
                         float* out_final,
-                        bool final_global) {
+                        bool final_global,
+                        int feature_stride) {
     int cur = 0;
     for (size_t l = 0; l < e->layers.size(); ++l) {
         const bool last = l + 1 == e->layers.size();
@@ -273,6 +343,9 @@ static void run_network(vm_engine* e,
         a.n_neighbours = n_neighbours;
         a.f0           = f0;
         a.out_global   = (last && final_global) ? 1 : 0;
+        a.in_stride    = feature_stride;
+        a.out_stride   = feature_stride;
+        a.out_planar   = (!last && e->layers[l].cout % 4 == 0) ? 1 : 0;
         launch_conv(e, e->layers[l], a, n_frames, max_rows, lane.stream);
         cur ^= 1;
     }
@@ -493,7 +566,7 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
                                                reinterpret_cast<float4*>(lane.d_feat[0].p));
             VM_CUDA(cudaGetLastError());
             end_stage(e, s);
-            run_network(e, lane, e->d_offsets.p, e->d_nb.p, N, f0, nf, max_rows, e->d_cls.p, true);
+            run_network(e, lane, e->d_offsets.p, e->d_nb.p, N, f0, nf, max_rows, e->d_cls.p, true, static_cast<int>(rows_cap));
         }
     }
     lane.busy = true;
@@ -622,6 +695,13 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
             VM_CUDA(cudaStreamSynchronize(e->lanes[l].stream));
             e->lanes[l].busy = false;
         }
+        if (*e->h_abort == tc::ABORT_TC_RANGE && e->use_tc) {
+            // a feature value beyond the range of the fp16 split: this engine goes back to the FFMA kernels for good and
+            // the batch is computed again
+            e->use_tc = false;
+            return run_batch(e, frames, n_frames, flags, out);
+        }
+        if (*e->h_abort == tc::ABORT_TC_TIMEOUT) return fail(VM_ERR_DEVICE_ABORT, "a tensor-core kernel gave up waiting on an mbarrier");
         if (*e->h_abort != 0) return fail(VM_ERR_DEVICE_ABORT, "a kernel gave up on a bounded loop (BSP deeper than 128 levels)");
 
         if (e->timing) {
@@ -715,6 +795,7 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
         VM_CUDA(cudaSetDevice(device));
         if (const char* v = std::getenv("VMCUDA_CHUNK_FRAMES")) e->chunk_frames = std::max(1, std::atoi(v));
         if (const char* v = std::getenv("VMCUDA_CHUNK_CANDIDATES")) e->chunk_candidates = std::max<long long>(1, std::atoll(v));
+        if (const char* v = std::getenv("VMCUDA_TC")) e->use_tc = std::atoi(v) != 0;
         if (const char* v = std::getenv("VMCUDA_LANES")) e->n_lanes = std::min(MAX_LANES, std::max(1, std::atoi(v)));
         for (int l = 0; l < MAX_LANES; ++l) {
             Lane& lane = e->lanes[l];
@@ -747,6 +828,50 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
                 for (int c = 0; c < L.n_out; ++c) packed[static_cast<size_t>(L.n_in) * d.coutp + c] = L.biases[c];
                 VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&d.d_weights), packed.size() * sizeof(float)));
                 VM_CUDA(cudaMemcpy(d.d_weights, packed.data(), packed.size() * sizeof(float), cudaMemcpyHostToDevice));
+                // tensor-core copy of the weights: per 16-byte K chunk, NP rows of hi parts then NP rows of lo parts
+                if ((width == 8 || width == 16 || width == 32) && L.n_out <= 32 && i == 0) {
+                    const int np    = L.n_out <= 16 ? 16 : 32;
+                    const int K     = L.n_in;
+                    const bool half = width != 8;
+                    const int kch   = half ? 8 : 4;
+                    float w_max     = 0.0f;
+                    for (size_t q = 0; q < size_t(K) * L.n_out; ++q) w_max = std::max(w_max, std::fabs(L.weights[q]));
+                    const size_t smem_need = 256 + size_t(9) * 2 * (width / kch) * 128 * 16 + size_t(K / kch) * 2 * np * 16;
+                    if (smem_need <= 200 * 1024 && (!half || w_max < 60000.0f)) {
+                        const size_t chunks = size_t(K / kch);
+                        std::vector<unsigned char> cat(chunks * 2 * np * 16, 0);
+                        std::vector<float> bias(np, 0.0f);
+                        for (int k = 0; k < K; ++k) {
+                            for (int n = 0; n < L.n_out; ++n) {
+                                const float w     = L.weights[size_t(k) * L.n_out + n];
+                                const size_t base = size_t(k / kch) * 2 * np * 16;
+                                if (half) {
+                                    const __half h = __float2half_rn(w);
+                                    const __half l = __float2half_rn(w - __half2float(h));
+                                    std::memcpy(&cat[base + size_t(n) * 16 + (k % kch) * 2], &h, 2);
+                                    std::memcpy(&cat[base + size_t(np + n) * 16 + (k % kch) * 2], &l, 2);
+                                }
+                                else {
+                                    uint32_t bits;
+                                    std::memcpy(&bits, &w, sizeof(bits));
+                                    bits &= 0xFFFFE000u;
+                                    float h;
+                                    std::memcpy(&h, &bits, sizeof(h));
+                                    const float l = w - h;
+                                    std::memcpy(&cat[base + size_t(n) * 16 + (k % kch) * 4], &h, 4);
+                                    std::memcpy(&cat[base + size_t(np + n) * 16 + (k % kch) * 4], &l, 4);
+                                }
+                            }
+                        }
+                        for (int n = 0; n < L.n_out; ++n) bias[n] = L.biases[n];
+                        VM_CUDA(cudaMalloc(&d.d_tc_cat, cat.size()));
+                        VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&d.d_tc_bias), bias.size() * sizeof(float)));
+                        VM_CUDA(cudaMemcpy(d.d_tc_cat, cat.data(), cat.size(), cudaMemcpyHostToDevice));
+                        VM_CUDA(cudaMemcpy(d.d_tc_bias, bias.data(), bias.size() * sizeof(float), cudaMemcpyHostToDevice));
+                        d.tc_np   = np;
+                        d.tc_half = half;
+                    }
+                }
                 e->layers.push_back(d);
                 width        = L.n_out;
                 e->max_width = std::max(e->max_width, width);
@@ -778,7 +903,11 @@ void vm_engine_destroy(vm_engine* e) {
     cudaSetDevice(e->device);
     cudaDeviceSynchronize();
     for (auto* m : e->meshes) free_mesh(m);
-    for (auto& L : e->layers) cudaFree(L.d_weights);
+    for (auto& L : e->layers) {
+        cudaFree(L.d_weights);
+        cudaFree(L.d_tc_cat);
+        cudaFree(L.d_tc_bias);
+    }
     for (auto& lane : e->lanes) {
         lane.h_frames.release();
         lane.d_frames.release();
@@ -975,7 +1104,7 @@ vm_status vm_network(vm_engine* e, const float* input, const int32_t* neighbourh
         VM_CUDA(cudaMemcpyAsync(e->d_nb.p, neighbourhood, sizeof(int32_t) * rows * n_neighbours, cudaMemcpyHostToDevice, lane.stream));
         VM_CUDA(cudaMemcpyAsync(lane.d_feat[0].p, input, sizeof(float) * rows * 4, cudaMemcpyHostToDevice, lane.stream));
         e->timing = false;
-        run_network(e, lane, e->d_offsets.p, e->d_nb.p, n_neighbours, 0, 1, n_rows, e->d_cls.p, true);
+        run_network(e, lane, e->d_offsets.p, e->d_nb.p, n_neighbours, 0, 1, n_rows, e->d_cls.p, true, n_rows);
         VM_CUDA(cudaMemcpyAsync(out, e->d_cls.p, sizeof(float) * rows * e->n_classes, cudaMemcpyDeviceToHost, lane.stream));
         VM_CUDA(cudaStreamSynchronize(lane.stream));
     }

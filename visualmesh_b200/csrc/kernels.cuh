@@ -322,9 +322,13 @@ __device__ __forceinline__ void activate(float* v, int act) {
 // ---- fused graph convolution layer -------------------------------------------------------------------------------
 // gather (cpp/visualmesh/engine/cpu/engine.hpp:216-235) + dense with the accumulator started at the bias and k
 // ascending (engine.hpp:250-256) + activation (engine.hpp:259), one launch per dense layer, nothing materialised.
+// Feature layout between layers. A width that is a multiple of 4 is stored "chunk-planar": float4 chunk c of row r at
+// float4 index c * stride + r, so that the 32 threads of a warp, which own 32 consecutive rows, read and write
+// consecutive 16-byte pieces (one 512-byte request per instruction instead of 32 pieces scattered over 16 cache
+// lines). Other widths, and the final classifications, are row-major [row][width].
 struct ConvArgs {
-    const float* in;        // chunk-local feature rows, CIN floats each
-    float* out;             // chunk-local feature rows, or the batch-wide classifications when out_global
+    const float* in;        // chunk-local features (planar when CIN % 4 == 0, else row-major)
+    float* out;             // chunk-local features, or the batch-wide row-major classifications when out_global
     const int32_t* nb;      // batch-wide neighbourhood rows (frame-local indices)
     const int32_t* offsets; // batch-wide point offsets
     const float* weights;   // [n_slots * CIN][COUTP] row-major, COUTP = COUT rounded up to 4, zero padded
@@ -334,12 +338,15 @@ struct ConvArgs {
     int32_t activation;
     int32_t f0;
     int32_t out_global;
+    int32_t in_stride;      // rows per planar chunk of `in`
+    int32_t out_stride;     // rows per planar chunk of `out`
+    int32_t out_planar;     // write `out` chunk-planar (needs COUT % 4 == 0 and !out_global)
 };
 
 // Each thread owns R rows strided by the block size, so a warp's loads and stores of one row index are contiguous.
 // The layer's weights sit in shared memory; every weight read is a 128-bit broadcast shared by the R rows.
-template <int CIN, int COUT, int R>
-__global__ void __launch_bounds__(CONV_THREADS) k_graph_conv(const ConvArgs a) {
+template <int CIN, int COUT, int R, int T = CONV_THREADS, int MINB = 1>
+__global__ void __launch_bounds__(T, MINB) k_graph_conv(const ConvArgs a) {
     constexpr int COUTP = (COUT + 3) & ~3;
     extern __shared__ float4 smem4[];
     float* w_s = reinterpret_cast<float*>(smem4);
@@ -348,14 +355,14 @@ __global__ void __launch_bounds__(CONV_THREADS) k_graph_conv(const ConvArgs a) {
     const int frame          = a.f0 + frame_in_chunk;
     const int start          = a.offsets[frame];
     const int rows           = a.offsets[frame + 1] - start + 1;
-    const int first          = blockIdx.x * (CONV_THREADS * R);
+    const int first          = blockIdx.x * (T * R);
     if (first >= rows) return;
 
     const int K = a.n_slots * CIN;
     {
         const float4* src = reinterpret_cast<const float4*>(a.weights);
         const int total4  = (K * COUTP + COUTP) / 4;  // weights then biases, contiguous on the device
-        for (int i = threadIdx.x; i < total4; i += CONV_THREADS) smem4[i] = __ldg(src + i);
+        for (int i = threadIdx.x; i < total4; i += T) smem4[i] = __ldg(src + i);
     }
     __syncthreads();
     const float* b_s = w_s + K * COUTP;
@@ -367,16 +374,19 @@ __global__ void __launch_bounds__(CONV_THREADS) k_graph_conv(const ConvArgs a) {
     float acc[R][COUTP];
 #pragma unroll
     for (int q = 0; q < R; ++q) {
-        row[q] = min(first + q * CONV_THREADS + static_cast<int>(threadIdx.x), rows - 1);
+        row[q] = min(first + q * T + static_cast<int>(threadIdx.x), rows - 1);
 #pragma unroll
         for (int j = 0; j < COUTP; ++j) acc[q][j] = b_s[j];
     }
 
+    const float4* in4 = reinterpret_cast<const float4*>(a.in);
     for (int s = 0; s < a.n_slots; ++s) {
         const float* src[R];
+        int src_row[R];
 #pragma unroll
         for (int q = 0; q < R; ++q) {
             const int idx = (s == 0) ? row[q] : __ldg(a.nb + (nb_base + row[q]) * a.n_neighbours + (s - 1));
+            src_row[q]    = local_base + idx;
             src[q]        = a.in + static_cast<size_t>(local_base + idx) * CIN;
         }
         const float* w_slot = w_s + s * CIN * COUTP;
@@ -385,7 +395,7 @@ __global__ void __launch_bounds__(CONV_THREADS) k_graph_conv(const ConvArgs a) {
             for (int c4 = 0; c4 < CIN / 4; ++c4) {
                 float4 x[R];
 #pragma unroll
-                for (int q = 0; q < R; ++q) x[q] = *reinterpret_cast<const float4*>(src[q] + c4 * 4);
+                for (int q = 0; q < R; ++q) x[q] = in4[static_cast<size_t>(c4) * a.in_stride + src_row[q]];
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     const float* w_row = w_slot + (c4 * 4 + kk) * COUTP;
@@ -429,11 +439,19 @@ __global__ void __launch_bounds__(CONV_THREADS) k_graph_conv(const ConvArgs a) {
     const size_t out_base = a.out_global ? nb_base : static_cast<size_t>(local_base);
 #pragma unroll
     for (int q = 0; q < R; ++q) {
-        const int i = first + q * CONV_THREADS + static_cast<int>(threadIdx.x);
+        const int i = first + q * T + static_cast<int>(threadIdx.x);
         if (i >= rows) continue;
         activate<COUT>(acc[q], a.activation);
         float* dst = a.out + (out_base + i) * COUT;
-        if (COUT % 4 == 0) {
+        if (COUT % 4 == 0 && a.out_planar) {
+            float4* out4 = reinterpret_cast<float4*>(a.out);
+#pragma unroll
+            for (int j4 = 0; j4 < COUT / 4; ++j4) {
+                out4[static_cast<size_t>(j4) * a.out_stride + out_base + i] =
+                  make_float4(acc[q][j4 * 4], acc[q][j4 * 4 + 1], acc[q][j4 * 4 + 2], acc[q][j4 * 4 + 3]);
+            }
+        }
+        else if (COUT % 4 == 0) {
 #pragma unroll
             for (int j4 = 0; j4 < COUT / 4; ++j4) {
                 *reinterpret_cast<float4*>(dst + j4 * 4) =
@@ -458,7 +476,16 @@ __global__ void __launch_bounds__(CONV_THREADS) k_graph_conv_generic(const ConvA
     const int local_base  = start - a.offsets[a.f0] + frame_in_chunk;
     const size_t nb_base  = static_cast<size_t>(start + frame);
     const size_t out_base = a.out_global ? nb_base : static_cast<size_t>(local_base);
-    float* dst            = a.out + (out_base + i) * cout;
+    const bool in_planar  = (cin % 4) == 0;
+    const bool out_planar = a.out_planar != 0;
+    // element c of a row in either layout
+    auto in_at = [&](size_t r, int c) -> float {
+        return in_planar ? a.in[((static_cast<size_t>(c >> 2) * a.in_stride + r) << 2) + (c & 3)] : a.in[r * cin + c];
+    };
+    auto out_ptr = [&](int c) -> float* {
+        return out_planar ? a.out + ((static_cast<size_t>(c >> 2) * a.out_stride + out_base + i) << 2) + (c & 3)
+                          : a.out + (out_base + i) * cout + c;
+    };
     const float* biases   = a.weights + static_cast<size_t>(a.n_slots) * cin * coutp;
     for (int j0 = 0; j0 < cout; j0 += 8) {
         float acc[8];
@@ -466,9 +493,9 @@ __global__ void __launch_bounds__(CONV_THREADS) k_graph_conv_generic(const ConvA
         for (int jj = 0; jj < 8; ++jj) acc[jj] = (j0 + jj < cout) ? __ldg(biases + j0 + jj) : 0.0f;
         for (int s = 0; s < a.n_slots; ++s) {
             const int idx    = (s == 0) ? i : __ldg(a.nb + (nb_base + i) * a.n_neighbours + (s - 1));
-            const float* src = a.in + static_cast<size_t>(local_base + idx) * cin;
+            const size_t src = static_cast<size_t>(local_base + idx);
             for (int c = 0; c < cin; ++c) {
-                const float x      = src[c];
+                const float x      = in_at(src, c);
                 const float* w_row = a.weights + static_cast<size_t>(s * cin + c) * coutp + j0;
 #pragma unroll
                 for (int jj = 0; jj < 8; ++jj) {
@@ -478,27 +505,27 @@ __global__ void __launch_bounds__(CONV_THREADS) k_graph_conv_generic(const ConvA
         }
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
-            if (j0 + jj < cout) dst[j0 + jj] = acc[jj];
+            if (j0 + jj < cout) *out_ptr(j0 + jj) = acc[jj];
         }
     }
     // activation over the row this thread has just written
     if (a.activation == VM_SELU) {
-        for (int j = 0; j < cout; ++j) dst[j] = selu(dst[j]);
+        for (int j = 0; j < cout; ++j) *out_ptr(j) = selu(*out_ptr(j));
     }
     else if (a.activation == VM_RELU) {
-        for (int j = 0; j < cout; ++j) dst[j] = (dst[j] < 0.0f) ? 0.0f : dst[j];
+        for (int j = 0; j < cout; ++j) *out_ptr(j) = (*out_ptr(j) < 0.0f) ? 0.0f : *out_ptr(j);
     }
     else if (a.activation == VM_TANH) {
-        for (int j = 0; j < cout; ++j) dst[j] = tanhf(dst[j]);
+        for (int j = 0; j < cout; ++j) *out_ptr(j) = tanhf(*out_ptr(j));
     }
     else if (a.activation == VM_SOFTMAX) {
         float total = 0.0f;
         for (int j = 0; j < cout; ++j) {
-            const float e = expf(dst[j]);
-            dst[j]        = e;
+            const float e = expf(*out_ptr(j));
+            *out_ptr(j)   = e;
             total         = __fadd_rn(total, e);
         }
-        for (int j = 0; j < cout; ++j) dst[j] = __fdiv_rn(dst[j], total);
+        for (int j = 0; j < cout; ++j) *out_ptr(j) = __fdiv_rn(*out_ptr(j), total);
     }
 }
 
