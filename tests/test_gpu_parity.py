@@ -238,3 +238,59 @@ def test_config3_dense_mesh_projection_and_two_layers():
     print(f"cfg3 (2 layers): {rep}")
     assert rep.ok and rep.n_ref > 900000, str(rep)
     engine.close()
+
+
+# ---- tensor-core graph convolution (tcgen05) ---------------------------------------------------------------------------
+
+def _engine_with_tc(network, mode):
+    import os
+    old = os.environ.get("VMCUDA_TC")
+    os.environ["VMCUDA_TC"] = str(mode)
+    try:
+        return Engine(network)
+    finally:
+        if old is None:
+            os.environ.pop("VMCUDA_TC")
+        else:
+            os.environ["VMCUDA_TC"] = old
+
+
+def _random_rows(n, n_neighbours, seed):
+    x = W.uniform(seed, n * 4, -1.0, 1.0).reshape(n, 4).astype(np.float32)
+    x[-1] = -1.0
+    nb = (W.splitmix64(seed + 1, n * n_neighbours) % np.uint64(n)).astype(np.int32).reshape(n, n_neighbours)
+    nb[-1] = n - 1
+    return x, nb
+
+
+@pytest.mark.parametrize("n_neighbours,widths", [(6, [16, 16, 16, 8, 8, 3]), (8, [32, 32, 32, 4]), (4, [16, 32, 16, 2])])
+def test_tensor_core_layers_match_the_oracle(n_neighbours, widths):
+    """Every layer shape that has a tcgen05 kernel (mode 2 forces them on), several tiles and a ragged last tile."""
+    net = W.make_network(7, n_neighbours, widths)
+    x, nb = _random_rows(1000, n_neighbours, 11)
+    want = O.network(x, nb, net)
+    for mode in (0, 2):
+        engine = _engine_with_tc(net, mode)
+        got = engine.network(x, nb)
+        d = np.abs(got.astype(np.float64) - want.astype(np.float64)).max()
+        print(f"N={n_neighbours} widths={widths} tensor-core mode {mode}: max |d| = {d:.3g}")
+        assert d <= P.TOL_CLS / 4
+        engine.close()
+
+
+def test_tensor_core_range_fallback():
+    """Features beyond the range of the fp16 split make the engine recompute with the FFMA kernels, transparently:
+    the result is bit for bit what an engine without tensor-core kernels returns."""
+    net = W.make_network(9, 6, [16, 16, 2])
+    net[0][0].weights[:] *= 3.0e5  # first layer output ~1e5: too large for fp16
+    net[1][0].weights[:] *= 1.0e-5
+    x, nb = _random_rows(700, 6, 13)
+    plain = _engine_with_tc(net, 0)
+    want = plain.network(x, nb)
+    plain.close()
+    assert np.all(np.isfinite(want))
+    engine = _engine_with_tc(net, 2)
+    for _ in range(2):  # the second call runs on the engine that has already fallen back
+        got = engine.network(x, nb)
+        assert np.array_equal(G.bits(got), G.bits(want))
+    engine.close()

@@ -26,7 +26,6 @@ namespace vm {
 namespace tc {
 
     constexpr int TILE_ROWS     = 128;
-    constexpr int THREADS       = 128;
     constexpr int MAX_FRAMES    = 64;       // frames per launch whose tile counts fit the shared prefix table
     constexpr uint32_t WAIT_LIMIT = 4000000;  // polls of mbarrier.try_wait before giving up
     constexpr int ABORT_TC_TIMEOUT = 2;
@@ -122,10 +121,30 @@ namespace tc {
                + static_cast<size_t>(n_slots) * (CIN / Format<HALF>::KCH) * 2 * NP * 16;
     }
 
+    __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+    }
+    // bounded wait that also gives up as soon as another role of the CTA has failed
+    __device__ __forceinline__ bool mbar_wait_or_fail(uint32_t bar, uint32_t parity, volatile int32_t* failed) {
+        for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+            if ((i & 1023u) == 1023u && *failed) return false;
+        }
+        return false;
+    }
+
+    constexpr int PRODUCER_WARPS = 4;
+    constexpr int CTA_THREADS    = (PRODUCER_WARPS + 1) * 32;
+
     // The two products of one K step:  D[:, 0:2NP] += A_hi . [B_hi | B_lo]   and   D[:, 0:NP] += A_lo . B_hi ;
     // the epilogue adds the two halves of D. A is read twice per K step instead of three times.
+    //
+    // Roles. Warps 0-3 (thread = row of the tile): gather, split, store into the stage, signal full[stage]; after the
+    // last slot of a tile they wait for its accumulator, read it, release it and write the output rows.
+    // Warp 4, one lane: waits full[stage], issues the stage's MMAs, commits to empty[stage] (the stage may be
+    // overwritten once they have read it) and after a tile's last slot to acc_full. No block-wide barrier in the loop.
     template <int CIN, int NP, int STAGES, int NSLOTS, bool HALF>
-    __global__ void __launch_bounds__(THREADS) k_graph_conv_tc(const ConvArgs a, const Args t) {
+    __global__ void __launch_bounds__(CTA_THREADS) k_graph_conv_tc(const ConvArgs a, const Args t) {
         static_assert(NP == 16 || NP == 32, "unsupported tile width");
         constexpr int KCH        = Format<HALF>::KCH;
         static_assert(CIN % (2 * KCH) == 0, "a slot must hold whole K steps");
@@ -134,22 +153,37 @@ namespace tc {
         constexpr int SLOT_BYTES = PLANES * PLANE;       // one slot, hi or lo
         constexpr int WCHUNK     = 2 * NP * 16;          // bytes of one weight chunk: hi rows then lo rows
         constexpr int TMEM_COLS  = 4 * NP;               // two accumulator buffers of 2 * NP columns
+        constexpr int DEPTH      = CIN <= 16 ? 2 : 1;    // slots whose loads are in flight ahead of the one being stored
 
         extern __shared__ __align__(1024) unsigned char smem_raw[];
-        __shared__ uint64_t bars[STAGES + 2];
+        // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+        __shared__ uint64_t bars[2 * STAGES + 4];
         __shared__ uint32_t tmem_base_slot;
         __shared__ int32_t tile_prefix[MAX_FRAMES + 1];
-        __shared__ int32_t failed;
+        __shared__ int32_t failed_s;
+        volatile int32_t* failed = &failed_s;
 
         const int tid  = threadIdx.x;
         const int warp = tid >> 5;
+        const int lane = tid & 31;
         unsigned char* stage_base = smem_raw;
         unsigned char* w_s        = smem_raw + static_cast<size_t>(STAGES) * 2 * SLOT_BYTES;
+        const uint32_t bar_full      = smem_u32(&bars[0]);
+        const uint32_t bar_empty     = smem_u32(&bars[STAGES]);
+        const uint32_t bar_acc_full  = smem_u32(&bars[2 * STAGES]);
+        const uint32_t bar_acc_empty = smem_u32(&bars[2 * STAGES + 2]);
 
         // ---- set-up ----
         if (tid == 0) {
-            failed = 0;
-            for (int i = 0; i < STAGES + 2; ++i) mbar_init(smem_u32(&bars[i]), 1);
+            failed_s = 0;
+            for (int i = 0; i < STAGES; ++i) {
+                mbar_init(bar_full + 8 * i, PRODUCER_WARPS);
+                mbar_init(bar_empty + 8 * i, 1);
+            }
+            for (int i = 0; i < 2; ++i) {
+                mbar_init(bar_acc_full + 8 * i, 1);
+                mbar_init(bar_acc_empty + 8 * i, PRODUCER_WARPS);
+            }
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             int run = 0;
             for (int f = 0; f < t.n_frames; ++f) {
@@ -167,7 +201,7 @@ namespace tc {
         {
             const uint4* g = reinterpret_cast<const uint4*>(t.w_cat);
             uint4* sw      = reinterpret_cast<uint4*>(w_s);
-            for (int i = tid; i < NSLOTS * PLANES * 2 * NP; i += THREADS) sw[i] = __ldg(g + i);
+            for (int i = tid; i < NSLOTS * PLANES * 2 * NP; i += CTA_THREADS) sw[i] = __ldg(g + i);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -175,130 +209,152 @@ namespace tc {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_base = tmem_base_slot;
         const int total_tiles    = tile_prefix[t.n_frames];
+        // tiles are dealt round-robin: a contiguous run per CTA was measured 10 % slower (the tail is less balanced)
+        bool out_of_range        = false;
 
-        // instruction descriptors: D = F32, A and B K-major, M = 128, N = 2 NP (hi | lo weights) or NP (hi weights)
-        constexpr uint32_t IDESC_BASE = (1u << 4) | (Format<HALF>::AB_CODE << 7) | (Format<HALF>::AB_CODE << 10) | (static_cast<uint32_t>(TILE_ROWS >> 4) << 24);
-        constexpr uint32_t IDESC_CAT  = IDESC_BASE | (static_cast<uint32_t>((2 * NP) >> 3) << 17);
-        constexpr uint32_t IDESC_HI   = IDESC_BASE | (static_cast<uint32_t>(NP >> 3) << 17);
-        const uint32_t w_addr = smem_u32(w_s);
-        const float4* in4     = reinterpret_cast<const float4*>(a.in);
-
-        uint32_t it         = 0;  // stage uses so far
-        uint32_t tile_count = 0;
-        bool ok             = true;
-        bool out_of_range   = false;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
-            int f = 0;
-            while (f + 1 < t.n_frames && tile_prefix[f + 1] <= tile) ++f;
-            const int frame      = a.f0 + f;
-            const int start      = a.offsets[frame];
-            const int rows       = a.offsets[frame + 1] - start + 1;
-            const int row        = (tile - tile_prefix[f]) * TILE_ROWS + tid;
-            const int rowc       = min(row, rows - 1);
-            const int local_base = start - a.offsets[a.f0] + f;
-            const size_t nb_base = static_cast<size_t>(start + frame);
-            const uint32_t acc   = tmem_base + (tile_count & 1u) * (2 * NP);
-
-            // all neighbour indices of this row up front, and the first slot's feature chunks: the loads of slot s + 1
-            // are in flight while slot s is split, stored and multiplied
-            int src_rows[NSLOTS];
-            src_rows[0] = local_base + rowc;
-#pragma unroll
-            for (int s = 1; s < NSLOTS; ++s) src_rows[s] = local_base + __ldg(a.nb + (nb_base + rowc) * a.n_neighbours + (s - 1));
-            constexpr int DEPTH = 1;  // slots whose loads are in flight ahead of the one being stored
-            float4 ring[DEPTH][CIN / 4];
-#pragma unroll
-            for (int d = 0; d < DEPTH; ++d) {
-                if (d < NSLOTS) {
-#pragma unroll
-                    for (int c = 0; c < CIN / 4; ++c) ring[d][c] = in4[static_cast<size_t>(c) * a.in_stride + src_rows[d]];
-                }
-            }
-
-#pragma unroll
-            for (int s = 0; s < NSLOTS; ++s, ++it) {
-                const uint32_t stage = it % STAGES;
-                const uint32_t use   = it / STAGES;
-                float4 cur[CIN / 4];
-#pragma unroll
-                for (int c = 0; c < CIN / 4; ++c) cur[c] = ring[s % DEPTH][c];
-                if (s + DEPTH < NSLOTS) {
-#pragma unroll
-                    for (int c = 0; c < CIN / 4; ++c) ring[s % DEPTH][c] = in4[static_cast<size_t>(c) * a.in_stride + src_rows[s + DEPTH]];
-                }
-                if (use > 0 && !mbar_wait(smem_u32(&bars[stage]), (use - 1) & 1u)) { atomicExch(&failed, 1); }
-                unsigned char* hi_p = stage_base + static_cast<size_t>(stage) * 2 * SLOT_BYTES;
-                unsigned char* lo_p = hi_p + SLOT_BYTES;
-                if (HALF) {
-#pragma unroll
-                    for (int p = 0; p < PLANES; ++p) {
-                        const float x[8] = {cur[2 * p].x, cur[2 * p].y, cur[2 * p].z, cur[2 * p].w,
-                                            cur[2 * p + 1].x, cur[2 * p + 1].y, cur[2 * p + 1].z, cur[2 * p + 1].w};
-                        uint32_t h[4], l[4];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            out_of_range |= fabsf(x[2 * q]) > 60000.0f || fabsf(x[2 * q + 1]) > 60000.0f;
-                            const __half h0 = __float2half_rn(x[2 * q]);
-                            const __half h1 = __float2half_rn(x[2 * q + 1]);
-                            const __half l0 = __float2half_rn(x[2 * q] - __half2float(h0));
-                            const __half l1 = __float2half_rn(x[2 * q + 1] - __half2float(h1));
-                            h[q] = static_cast<uint32_t>(__half_as_ushort(h0)) | (static_cast<uint32_t>(__half_as_ushort(h1)) << 16);
-                            l[q] = static_cast<uint32_t>(__half_as_ushort(l0)) | (static_cast<uint32_t>(__half_as_ushort(l1)) << 16);
+        if (warp == PRODUCER_WARPS) {
+            // ================= MMA issuer =================
+            if (lane == 0) {
+                constexpr uint32_t IDESC_BASE = (1u << 4) | (Format<HALF>::AB_CODE << 7) | (Format<HALF>::AB_CODE << 10) | (static_cast<uint32_t>(TILE_ROWS >> 4) << 24);
+                constexpr uint32_t IDESC_CAT  = IDESC_BASE | (static_cast<uint32_t>((2 * NP) >> 3) << 17);
+                constexpr uint32_t IDESC_HI   = IDESC_BASE | (static_cast<uint32_t>(NP >> 3) << 17);
+                const uint32_t w_addr = smem_u32(w_s);
+                const uint32_t a_addr = smem_u32(stage_base);
+                uint32_t it = 0, tile_count = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
+                    const uint32_t ab  = tile_count & 1u;
+                    const uint32_t acc = tmem_base + ab * (2 * NP);
+                    // the epilogue of the tile that used this accumulator two tiles ago must have read it
+                    if (tile_count >= 2 && !mbar_wait_or_fail(bar_acc_empty + 8 * ab, ((tile_count >> 1) - 1) & 1u, failed)) {
+                        ok = false;
+                        break;
+                    }
+                    for (int s = 0; s < NSLOTS; ++s, ++it) {
+                        const uint32_t stage = it % STAGES;
+                        const uint32_t use   = it / STAGES;
+                        if (!mbar_wait_or_fail(bar_full + 8 * stage, use & 1u, failed)) {
+                            ok = false;
+                            break;
                         }
-                        *reinterpret_cast<uint4*>(hi_p + p * PLANE + tid * 16) = make_uint4(h[0], h[1], h[2], h[3]);
-                        *reinterpret_cast<uint4*>(lo_p + p * PLANE + tid * 16) = make_uint4(l[0], l[1], l[2], l[3]);
-                    }
-                }
-                else {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t a_hi = a_addr + stage * 2 * SLOT_BYTES;
+                        const uint32_t a_lo = a_hi + SLOT_BYTES;
 #pragma unroll
-                    for (int c = 0; c < CIN / 4; ++c) {
-                        const float4 x = cur[c];
-                        float4 h, l;
-                        h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
-                        h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
-                        h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
-                        h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
-                        l.x = x.x - h.x;
-                        l.y = x.y - h.y;
-                        l.z = x.z - h.z;
-                        l.w = x.w - h.w;
-                        *reinterpret_cast<float4*>(hi_p + c * PLANE + tid * 16) = h;
-                        *reinterpret_cast<float4*>(lo_p + c * PLANE + tid * 16) = l;
+                        for (int ks = 0; ks < PLANES / 2; ++ks) {
+                            const uint64_t da_hi = smem_desc(a_hi + ks * 2 * PLANE, PLANE, 128);
+                            const uint64_t da_lo = smem_desc(a_lo + ks * 2 * PLANE, PLANE, 128);
+                            const uint64_t db    = smem_desc(w_addr + (s * PLANES + ks * 2) * WCHUNK, WCHUNK, 128);
+                            mma<HALF>(acc, da_hi, db, IDESC_CAT, (s == 0 && ks == 0) ? 0u : 1u);
+                            mma<HALF>(acc, da_lo, db, IDESC_HI, 1u);
+                        }
+                        commit(bar_empty + 8 * stage);
+                        if (s == NSLOTS - 1) commit(bar_acc_full + 8 * ab);
                     }
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                __syncthreads();
-                if (failed) {
-                    ok = false;
-                    break;
-                }
-                if (tid == 0) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a_hi = smem_u32(hi_p);
-                    const uint32_t a_lo = smem_u32(lo_p);
-#pragma unroll
-                    for (int ks = 0; ks < PLANES / 2; ++ks) {
-                        const uint64_t da_hi = smem_desc(a_hi + ks * 2 * PLANE, PLANE, 128);
-                        const uint64_t da_lo = smem_desc(a_lo + ks * 2 * PLANE, PLANE, 128);
-                        const uint64_t db    = smem_desc(w_addr + (s * PLANES + ks * 2) * WCHUNK, WCHUNK, 128);
-                        mma<HALF>(acc, da_hi, db, IDESC_CAT, (s == 0 && ks == 0) ? 0u : 1u);
-                        mma<HALF>(acc, da_lo, db, IDESC_HI, 1u);
-                    }
-                    commit(smem_u32(&bars[stage]));
-                    if (s == NSLOTS - 1) commit(smem_u32(&bars[STAGES + (tile_count & 1u)]));
-                }
+                if (!ok) failed_s = 1;
             }
-            if (!ok) break;
+        }
+        else {
+            // ================= producers + epilogue =================
+            const float4* in4 = reinterpret_cast<const float4*>(a.in);
+            uint32_t it = 0, tile_count = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
+                int f = 0;
+                while (f + 1 < t.n_frames && tile_prefix[f + 1] <= tile) ++f;
+                const int frame      = a.f0 + f;
+                const int start      = a.offsets[frame];
+                const int rows       = a.offsets[frame + 1] - start + 1;
+                const int row        = (tile - tile_prefix[f]) * TILE_ROWS + tid;
+                const int rowc       = min(row, rows - 1);
+                const int local_base = start - a.offsets[a.f0] + f;
+                const size_t nb_base = static_cast<size_t>(start + frame);
+                const uint32_t ab    = tile_count & 1u;
+                const uint32_t acc   = tmem_base + ab * (2 * NP);
 
-            // ---- epilogue: accumulator -> registers -> bias, activation -> global ----
-            // the decision to go on must be the same in every thread: the tensor-memory load below is warp-collective
-            const bool arrived = mbar_wait(smem_u32(&bars[STAGES + (tile_count & 1u)]), (tile_count >> 1) & 1u);
-            ok                 = __syncthreads_and(arrived ? 1 : 0) != 0;
-            if (!ok && tid == 0) failed = 1;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float v[NP];
-            if (ok) {
+                // all neighbour indices of this row up front; the loads of the next DEPTH slots are in flight while a slot
+                // is split and stored
+                int src_rows[NSLOTS];
+                src_rows[0] = local_base + rowc;
+#pragma unroll
+                for (int s = 1; s < NSLOTS; ++s) src_rows[s] = local_base + __ldg(a.nb + (nb_base + rowc) * a.n_neighbours + (s - 1));
+                float4 ring[DEPTH][CIN / 4];
+#pragma unroll
+                for (int d = 0; d < DEPTH; ++d) {
+                    if (d < NSLOTS) {
+#pragma unroll
+                        for (int c = 0; c < CIN / 4; ++c) ring[d][c] = in4[static_cast<size_t>(c) * a.in_stride + src_rows[d]];
+                    }
+                }
+
+#pragma unroll
+                for (int s = 0; s < NSLOTS; ++s, ++it) {
+                    const uint32_t stage = it % STAGES;
+                    const uint32_t use   = it / STAGES;
+                    float4 cur[CIN / 4];
+#pragma unroll
+                    for (int c = 0; c < CIN / 4; ++c) cur[c] = ring[s % DEPTH][c];
+                    if (s + DEPTH < NSLOTS) {
+#pragma unroll
+                        for (int c = 0; c < CIN / 4; ++c) ring[s % DEPTH][c] = in4[static_cast<size_t>(c) * a.in_stride + src_rows[s + DEPTH]];
+                    }
+                    // the MMAs that read this stage on its previous use must be done
+                    if (use > 0 && !mbar_wait_or_fail(bar_empty + 8 * stage, (use - 1) & 1u, failed)) ok = false;
+                    unsigned char* hi_p = stage_base + static_cast<size_t>(stage) * 2 * SLOT_BYTES;
+                    unsigned char* lo_p = hi_p + SLOT_BYTES;
+                    if (HALF) {
+#pragma unroll
+                        for (int p = 0; p < PLANES; ++p) {
+                            const float x[8] = {cur[2 * p].x, cur[2 * p].y, cur[2 * p].z, cur[2 * p].w,
+                                                cur[2 * p + 1].x, cur[2 * p + 1].y, cur[2 * p + 1].z, cur[2 * p + 1].w};
+                            uint32_t h[4], l[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                out_of_range |= fabsf(x[2 * q]) > 60000.0f || fabsf(x[2 * q + 1]) > 60000.0f;
+                                const __half h0 = __float2half_rn(x[2 * q]);
+                                const __half h1 = __float2half_rn(x[2 * q + 1]);
+                                const __half l0 = __float2half_rn(x[2 * q] - __half2float(h0));
+                                const __half l1 = __float2half_rn(x[2 * q + 1] - __half2float(h1));
+                                h[q] = static_cast<uint32_t>(__half_as_ushort(h0)) | (static_cast<uint32_t>(__half_as_ushort(h1)) << 16);
+                                l[q] = static_cast<uint32_t>(__half_as_ushort(l0)) | (static_cast<uint32_t>(__half_as_ushort(l1)) << 16);
+                            }
+                            *reinterpret_cast<uint4*>(hi_p + p * PLANE + tid * 16) = make_uint4(h[0], h[1], h[2], h[3]);
+                            *reinterpret_cast<uint4*>(lo_p + p * PLANE + tid * 16) = make_uint4(l[0], l[1], l[2], l[3]);
+                        }
+                    }
+                    else {
+#pragma unroll
+                        for (int c = 0; c < CIN / 4; ++c) {
+                            const float4 x = cur[c];
+                            float4 h, l;
+                            h.x = __uint_as_float(__float_as_uint(x.x) & 0xFFFFE000u);
+                            h.y = __uint_as_float(__float_as_uint(x.y) & 0xFFFFE000u);
+                            h.z = __uint_as_float(__float_as_uint(x.z) & 0xFFFFE000u);
+                            h.w = __uint_as_float(__float_as_uint(x.w) & 0xFFFFE000u);
+                            l.x = x.x - h.x;
+                            l.y = x.y - h.y;
+                            l.z = x.z - h.z;
+                            l.w = x.w - h.w;
+                            *reinterpret_cast<float4*>(hi_p + c * PLANE + tid * 16) = h;
+                            *reinterpret_cast<float4*>(lo_p + c * PLANE + tid * 16) = l;
+                        }
+                    }
+                    // make this warp's stores visible to the tensor core, then one arrival per warp
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * stage);
+                }
+                ok = __all_sync(0xffffffffu, ok) && !*failed;
+                if (!ok) break;
+
+                // ---- epilogue: accumulator -> registers -> bias, activation -> global ----
+                // the tensor-memory load is warp-collective: the warp decides together whether to go on
+                const bool arrived = mbar_wait_or_fail(bar_acc_full + 8 * ab, (tile_count >> 1) & 1u, failed);
+                ok                 = __all_sync(0xffffffffu, arrived);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float v[NP];
 #pragma unroll
                 for (int j0 = 0; j0 < 2 * NP; j0 += 16) {
                     uint32_t r[16];
@@ -318,7 +374,10 @@ namespace tc {
                         }
                     }
                 }
+                // the accumulator buffer may be overwritten from here on
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty + 8 * ab);
 #pragma unroll
                 for (int j = 0; j < NP; ++j) v[j] = v[j] + __ldg(t.bias + j);
                 if (row < rows) {
@@ -361,13 +420,14 @@ namespace tc {
                     }
                 }
             }
+            if (!ok && lane == 0) failed_s = 1;
         }
 
         // ---- tear-down: nothing of this CTA may still be running on the tensor core when its memory goes away ----
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         const int any_range = __syncthreads_or(out_of_range ? 1 : 0);
         if (tid == 0) {
-            if (failed) { atomicExch(t.abort_flag, ABORT_TC_TIMEOUT); }
+            if (failed_s) { atomicExch(t.abort_flag, ABORT_TC_TIMEOUT); }
             else if (any_range) {
                 atomicCAS(t.abort_flag, 0, ABORT_TC_RANGE);
             }

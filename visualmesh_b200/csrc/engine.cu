@@ -187,7 +187,8 @@ struct vm_engine {
     bool timing        = false;
     std::vector<std::pair<const char*, float>> stage_ms;
     int64_t launches = 0;
-    bool use_tc      = false;
+    bool use_tc      = true;
+    int tc_mode      = 1;
     cudaEvent_t ev_timer_start = nullptr, ev_timer_stop = nullptr;
 };
 
@@ -230,22 +231,6 @@ static void launch_conv_t(const ConvArgs& a, dim3 grid_rows, int max_rows, cudaS
 static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, int max_rows, cudaStream_t s) {
     const size_t smem = (static_cast<size_t>(a.n_slots) * L.cin * L.coutp + L.coutp) * sizeof(float);
     if (smem > 96 * 1024) return false;
-    static const int variant = [] {
-        const char* v = std::getenv("VMCUDA_CONV_VARIANT");
-        return v != nullptr ? std::atoi(v) : 0;
-    }();
-    if (L.cin == 16 && L.cout == 16 && variant != 0) {
-        switch (variant) {
-            case 1: launch_conv_t<16, 16, 2, 128, 1>(a, grid, max_rows, s); return true;
-            case 2: launch_conv_t<16, 16, 2, 256, 1>(a, grid, max_rows, s); return true;
-            case 3: launch_conv_t<16, 16, 4, 256, 1>(a, grid, max_rows, s); return true;
-            case 4: launch_conv_t<16, 16, 4, 128, 4>(a, grid, max_rows, s); return true;
-            case 5: launch_conv_t<16, 16, 1, 256, 1>(a, grid, max_rows, s); return true;
-            case 6: launch_conv_t<16, 16, 2, 128, 6>(a, grid, max_rows, s); return true;
-            case 7: launch_conv_t<16, 16, 8, 64, 1>(a, grid, max_rows, s); return true;
-            default: break;
-        }
-    }
 #define VM_CONV(CI, CO, RR)                                   \
     if (L.cin == CI && L.cout == CO) {                        \
         launch_conv_t<CI, CO, RR>(a, grid, max_rows, s);      \
@@ -263,7 +248,7 @@ static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, 
 
 template <int CIN, int NP, int NSLOTS, bool HALF>
 static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
-    constexpr int STAGES = NSLOTS * CIN <= 160 ? NSLOTS : 3;
+    constexpr int STAGES = 3;
     const size_t smem    = tc::smem_bytes<CIN, NP, STAGES, HALF>(NSLOTS);
     static int ctas_per_sm = 0;
     static int n_sms       = 0;
@@ -275,7 +260,11 @@ static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frame
         // resident CTAs per SM: shared memory (about 220 KB usable, some per CTA reserved) and tensor memory (512 columns)
         const int by_smem = static_cast<int>((220 * 1024) / (smem + 2048));
         const int by_tmem = 512 / (4 * NP);
-        ctas_per_sm       = std::max(1, std::min(std::min(by_smem, by_tmem), 6));
+        cudaFuncAttributes attr;
+        VM_CUDA(cudaFuncGetAttributes(&attr, tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF>));
+        const int regs_per_cta = ((attr.numRegs + 7) / 8 * 8) * tc::CTA_THREADS;
+        const int by_regs      = 65536 / std::max(1, regs_per_cta);
+        ctas_per_sm            = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
     }
     tc::Args t{};
     t.w_cat      = L.d_tc_cat;
@@ -285,11 +274,14 @@ static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frame
     t.abort_flag = abort_flag;
     const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
     const int grid        = std::max(1, std::min(tiles_upper, n_sms * ctas_per_sm));
-    tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF><<<grid, tc::THREADS, smem, s>>>(a, t);
+    tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
 }
 
 static bool launch_conv_tc(vm_engine* e, const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, cudaStream_t s) {
     if (L.tc_np == 0 || n_frames > tc::MAX_FRAMES) return false;
+    // mode 1 (default): only where the contraction is dense enough to pay - measured: 32-wide layers 1.7x faster than
+    // the FFMA kernel, 16 x 16 a tie, narrower layers slower; mode 2: wherever a tensor-core kernel exists
+    if (e->tc_mode == 1 && L.cin * L.cout < 512) return false;
 #define VM_TC(CI, NPAD, NS, HF)                                                      \
     if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS && L.tc_half == HF) {        \
         launch_conv_tc_t<CI, NPAD, NS, HF>(L, a, n_frames, max_rows, e->d_abort, s);   \
@@ -795,7 +787,10 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
         VM_CUDA(cudaSetDevice(device));
         if (const char* v = std::getenv("VMCUDA_CHUNK_FRAMES")) e->chunk_frames = std::max(1, std::atoi(v));
         if (const char* v = std::getenv("VMCUDA_CHUNK_CANDIDATES")) e->chunk_candidates = std::max<long long>(1, std::atoll(v));
-        if (const char* v = std::getenv("VMCUDA_TC")) e->use_tc = std::atoi(v) != 0;
+        if (const char* v = std::getenv("VMCUDA_TC")) {
+            e->tc_mode = std::atoi(v);
+            e->use_tc  = e->tc_mode != 0;
+        }
         if (const char* v = std::getenv("VMCUDA_LANES")) e->n_lanes = std::min(MAX_LANES, std::max(1, std::atoi(v)));
         for (int l = 0; l < MAX_LANES; ++l) {
             Lane& lane = e->lanes[l];
@@ -1104,9 +1099,19 @@ vm_status vm_network(vm_engine* e, const float* input, const int32_t* neighbourh
         VM_CUDA(cudaMemcpyAsync(e->d_nb.p, neighbourhood, sizeof(int32_t) * rows * n_neighbours, cudaMemcpyHostToDevice, lane.stream));
         VM_CUDA(cudaMemcpyAsync(lane.d_feat[0].p, input, sizeof(float) * rows * 4, cudaMemcpyHostToDevice, lane.stream));
         e->timing = false;
-        run_network(e, lane, e->d_offsets.p, e->d_nb.p, n_neighbours, 0, 1, n_rows, e->d_cls.p, true, n_rows);
-        VM_CUDA(cudaMemcpyAsync(out, e->d_cls.p, sizeof(float) * rows * e->n_classes, cudaMemcpyDeviceToHost, lane.stream));
-        VM_CUDA(cudaStreamSynchronize(lane.stream));
+        for (int attempt = 0; attempt < 2; ++attempt) {
+            VM_CUDA(cudaMemsetAsync(e->d_abort, 0, sizeof(int32_t), lane.stream));
+            run_network(e, lane, e->d_offsets.p, e->d_nb.p, n_neighbours, 0, 1, n_rows, e->d_cls.p, true, n_rows);
+            VM_CUDA(cudaMemcpyAsync(out, e->d_cls.p, sizeof(float) * rows * e->n_classes, cudaMemcpyDeviceToHost, lane.stream));
+            VM_CUDA(cudaMemcpyAsync(e->h_abort, e->d_abort, sizeof(int32_t), cudaMemcpyDeviceToHost, lane.stream));
+            VM_CUDA(cudaStreamSynchronize(lane.stream));
+            if (*e->h_abort == tc::ABORT_TC_RANGE && e->use_tc) {
+                e->use_tc = false;  // a value beyond the fp16 split's range: recompute with the FFMA kernels
+                continue;
+            }
+            if (*e->h_abort != 0) return fail(VM_ERR_DEVICE_ABORT, "a kernel gave up on a bounded wait");
+            break;
+        }
     }
     catch (const CudaFailure& f) {
         cudaGetLastError();
