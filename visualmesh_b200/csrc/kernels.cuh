@@ -465,6 +465,93 @@ __global__ void __launch_bounds__(T, MINB) k_graph_conv(const ConvArgs a) {
     }
 }
 
+// The same layer with the weights in the kernel's parameter space (constant bank) instead of shared memory: every
+// weight read is a constant-cache load that all lanes share and does not touch the L1/shared data path that the
+// gather loads. Layers whose weights fit the parameter space (WMAX floats).
+template <int WMAX>
+struct ConvWeights {
+    float w[WMAX];
+};
+
+template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS>
+__global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __grid_constant__ ConvWeights<WMAX> wp) {
+    static_assert(CIN % 4 == 0, "vector loads of the input rows");
+    constexpr int COUTP = (COUT + 3) & ~3;
+    const int frame_in_chunk = blockIdx.y;
+    const int frame          = a.f0 + frame_in_chunk;
+    const int start          = a.offsets[frame];
+    const int rows           = a.offsets[frame + 1] - start + 1;
+    const int first          = blockIdx.x * (T * R);
+    if (first >= rows) return;
+    const int K           = a.n_slots * CIN;
+    const int local_base  = start - a.offsets[a.f0] + frame_in_chunk;
+    const size_t nb_base  = static_cast<size_t>(start + frame);
+
+    int row[R];
+    float acc[R][COUTP];
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+        row[q] = min(first + q * T + static_cast<int>(threadIdx.x), rows - 1);
+#pragma unroll
+        for (int j = 0; j < COUTP; ++j) acc[q][j] = wp.w[K * COUTP + j];
+    }
+    const float4* in4 = reinterpret_cast<const float4*>(a.in);
+    for (int s = 0; s < a.n_slots; ++s) {
+        int src_row[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q) {
+            const int idx = (s == 0) ? row[q] : __ldg(a.nb + (nb_base + row[q]) * a.n_neighbours + (s - 1));
+            src_row[q]    = local_base + idx;
+        }
+        const int w_slot = s * CIN * COUTP;
+#pragma unroll
+        for (int c4 = 0; c4 < CIN / 4; ++c4) {
+            float4 x[R];
+#pragma unroll
+            for (int q = 0; q < R; ++q) x[q] = in4[static_cast<size_t>(c4) * a.in_stride + src_row[q]];
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+#pragma unroll
+                for (int j = 0; j < COUTP; ++j) {
+                    const float w = wp.w[w_slot + (c4 * 4 + kk) * COUTP + j];
+#pragma unroll
+                    for (int q = 0; q < R; ++q) {
+                        const float xv = kk == 0 ? x[q].x : kk == 1 ? x[q].y : kk == 2 ? x[q].z : x[q].w;
+                        acc[q][j]      = fmaf(xv, w, acc[q][j]);
+                    }
+                }
+            }
+        }
+    }
+    const size_t out_base = a.out_global ? nb_base : static_cast<size_t>(local_base);
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+        const int i = first + q * T + static_cast<int>(threadIdx.x);
+        if (i >= rows) continue;
+        activate<COUT>(acc[q], a.activation);
+        float* dst = a.out + (out_base + i) * COUT;
+        if (COUT % 4 == 0 && a.out_planar) {
+            float4* out4 = reinterpret_cast<float4*>(a.out);
+#pragma unroll
+            for (int j4 = 0; j4 < COUT / 4; ++j4) {
+                out4[static_cast<size_t>(j4) * a.out_stride + out_base + i] =
+                  make_float4(acc[q][j4 * 4], acc[q][j4 * 4 + 1], acc[q][j4 * 4 + 2], acc[q][j4 * 4 + 3]);
+            }
+        }
+        else if (COUT % 4 == 0) {
+#pragma unroll
+            for (int j4 = 0; j4 < COUT / 4; ++j4) {
+                *reinterpret_cast<float4*>(dst + j4 * 4) =
+                  make_float4(acc[q][j4 * 4], acc[q][j4 * 4 + 1], acc[q][j4 * 4 + 2], acc[q][j4 * 4 + 3]);
+            }
+        }
+        else {
+#pragma unroll
+            for (int j = 0; j < COUT; ++j) dst[j] = acc[q][j];
+        }
+    }
+}
+
 // Any layer shape: one row per thread, outputs in tiles of 8, weights read through the read-only cache.
 __global__ void __launch_bounds__(CONV_THREADS) k_graph_conv_generic(const ConvArgs a, int32_t cin, int32_t cout, int32_t coutp) {
     const int frame_in_chunk = blockIdx.y;
