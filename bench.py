@@ -37,7 +37,7 @@ from visualmesh_b200 import workloads as W  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture summarised in
 # profiles/ (None until captured); scaled to the launch's rows when the capture ran a smaller case.
-NCU_TRAFFIC_BYTES_PER_ROW = 118.4  # profiles/graph_conv_16x16_cfg1_16frames.md: 131.2 MB over 1,108,261 rows
+NCU_TRAFFIC_BYTES_PER_ROW = 119.4  # profiles/graph_conv_16x16_cfg1_16frames.md: 132.4 MB over 1,108,261 rows
 
 
 def _peaks():
@@ -359,10 +359,10 @@ def run_ours(args, rank, world, local_rank):
                        "on_screen_nodes_per_frame": points / args.steps / per_gpu,
                        "lookup": "device BSP walk", "l2": "inputs_larger_than_l2",
                        "distortion": "k_px = (k1/W^2, k2/W^4)", "parallelism": f"frame-sharded x{world}"},
-            "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": int(sum(sizes)),
-                    "d2h_bytes_per_step": int(d2h), "ms_per_step": 1e3 * e2e_elapsed / args.steps,
+            "e2e": {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": int(sum(sizes)) * world,
+                    "d2h_bytes_per_step": int(d2h) * world, "ms_per_step": 1e3 * e2e_elapsed / args.steps,
                     "engine_instances": n_inst},
-            "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+            "gpu_launches": int(launches) * world, "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
             "stages": stages, "wall_ms_per_step": 1e3 * wall / args.steps,
         }
         print(json.dumps(line), flush=True)

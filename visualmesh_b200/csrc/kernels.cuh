@@ -473,7 +473,7 @@ struct ConvWeights {
     float w[WMAX];
 };
 
-template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS>
+template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS, int NSLOTS = 0>
 __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __grid_constant__ ConvWeights<WMAX> wp) {
     static_assert(CIN % 4 == 0, "vector loads of the input rows");
     constexpr int COUTP = (COUT + 3) & ~3;
@@ -483,7 +483,9 @@ __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __g
     const int rows           = a.offsets[frame + 1] - start + 1;
     const int first          = blockIdx.x * (T * R);
     if (first >= rows) return;
-    const int K           = a.n_slots * CIN;
+    // NSLOTS > 0: the slot loop is unrolled and every weight is an immediate constant-bank operand of its FFMA
+    const int n_slots     = NSLOTS > 0 ? NSLOTS : a.n_slots;
+    const int K           = n_slots * CIN;
     const int local_base  = start - a.offsets[a.f0] + frame_in_chunk;
     const size_t nb_base  = static_cast<size_t>(start + frame);
 
@@ -496,7 +498,8 @@ __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __g
         for (int j = 0; j < COUTP; ++j) acc[q][j] = wp.w[K * COUTP + j];
     }
     const float4* in4 = reinterpret_cast<const float4*>(a.in);
-    for (int s = 0; s < a.n_slots; ++s) {
+#pragma unroll(NSLOTS > 0 ? NSLOTS : 1)
+    for (int s = 0; s < n_slots; ++s) {
         int src_row[R];
 #pragma unroll
         for (int q = 0; q < R; ++q) {
