@@ -294,3 +294,44 @@ def test_tensor_core_range_fallback():
         got = engine.network(x, nb)
         assert np.array_equal(G.bits(got), G.bits(want))
     engine.close()
+
+
+def test_network_shaped_like_the_reference_example_model(cases):
+    """13 groups with the layer shapes of the reference's example/model.yaml (28x16, 5 x 112x16, 112x8, 5 x 56x8,
+    56x5 softmax), seeded weights, on the reference's sampled inputs and neighbourhood."""
+    case = cases["ring6_equisolid_rgba"]
+    net = W.make_network(21, 6, [16] * 6 + [8] * 6 + [5])
+    engine = Engine(net)
+    for fr in case.frames[:2]:
+        sampled = O.interpolate(fr["pixel_coordinates"], fr["image"], *case.lens.dimensions, case.format)
+        inputs = np.concatenate([sampled, -np.ones((1, 4), np.float32)])
+        want = O.network(inputs, fr["neighbourhood"], net)
+        got = engine.network(inputs, fr["neighbourhood"])
+        assert got.shape == want.shape and got.shape[1] == 5
+        assert np.abs(got.astype(np.float64) - want.astype(np.float64)).max() <= P.TOL_CLS
+    engine.close()
+
+
+def test_visualmesh_height_table_through_the_engine():
+    """The VisualMesh overloads (cpp/visualmesh/engine/cpu/engine.hpp:160-165, :289-296): the engine picks the table
+    nearest to Hoc[2][3] and gives what a call on that Mesh gives."""
+    from visualmesh_b200.engine import VisualMesh
+    import math
+    vm = VisualMesh("RING6", "SPHERE", 0.0949, 0.0, 0.6, 1.4, 2.0, 0.5, 5.0)
+    net = W.make_network(3, 6, [8, 2])
+    engine = Engine(net)
+    lens = W.Lens((160, 128), W.EQUISOLID, 56.0, (0.0, 0.0), (0.0, 0.0), math.pi)
+    image = W.random_bytes(5, 160 * 128 * 4)
+    for h in (0.55, 0.93, 1.7):
+        Hoc = W.make_Hoc(math.radians(-50), math.radians(4), h)
+        a = engine(vm, Hoc, lens, image, W.fourcc("RGBA"))
+        mesh = vm.height(h)
+        b = engine(mesh, Hoc, lens, image, W.fourcc("RGBA"), ranges="device")
+        ranges = mesh.lookup(Hoc, lens)
+        want = O.classify(mesh.rays, mesh.neighbours, ranges, net, Hoc, lens, image, W.fourcc("RGBA"))
+        assert len(a.global_indices) > 50
+        for key in ("global_indices", "neighbourhood", "pixel_coordinates", "classifications"):
+            assert np.array_equal(G.bits(getattr(a, key)), G.bits(getattr(b, key))), key
+        rep = P.compare(a, want, lens.dimensions)
+        assert rep.ok, str(rep)
+    engine.close()

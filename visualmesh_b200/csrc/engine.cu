@@ -167,6 +167,7 @@ struct vm_engine {
     int n_lanes = vm::MAX_LANES;
     int64_t chunk_candidates = 2 << 20;
     int chunk_frames         = 16;
+    bool chunk_override      = false;  // set by the environment: use the limits above for every batch
     // batch-wide results
     vm::DeviceArray<int32_t> d_offsets;
     vm::PinnedArray<int32_t> h_offsets;
@@ -673,14 +674,20 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
         VM_CUDA(cudaMemsetAsync(e->d_offsets.p, 0, sizeof(int32_t), e->lanes[0].stream));
         VM_CUDA(cudaMemsetAsync(e->d_abort, 0, sizeof(int32_t), e->lanes[0].stream));
 
-        // chunks: runs of frames bounded by a candidate budget and a frame count
+        // chunks: runs of frames bounded by a candidate budget and a frame count. Small chunks let the copies of one
+        // chunk overlap the kernels of another; when there is nothing to copy in (frames already on the device, or
+        // projection only) larger chunks mean fewer, fuller launches.
+        bool host_images = false;
+        for (int f = 0; f < n_frames; ++f) host_images = host_images || (classify && !frames[f].image_on_device);
+        const int64_t max_chunk_candidates = (e->chunk_override || host_images) ? e->chunk_candidates : 4 * e->chunk_candidates;
+        const int max_chunk_frames         = (e->chunk_override || host_images) ? e->chunk_frames : std::min(4 * e->chunk_frames, static_cast<int>(tc::MAX_FRAMES));
         int f0 = 0, chunk = 0;
         Lane* prev = nullptr;
         std::vector<Lane*> order;
         while (f0 < n_frames) {
             int f1 = f0;
             int64_t c = 0;
-            while (f1 < n_frames && (f1 == f0 || (c + frame_candidates(frames[f1]) <= e->chunk_candidates && f1 - f0 < e->chunk_frames))) {
+            while (f1 < n_frames && (f1 == f0 || (c + frame_candidates(frames[f1]) <= max_chunk_candidates && f1 - f0 < max_chunk_frames))) {
                 c += frame_candidates(frames[f1]);
                 ++f1;
             }
@@ -808,8 +815,14 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
         if (device >= count) return fail(VM_ERR_INVALID_ARGUMENT, "no such device");
         e->device = device;
         VM_CUDA(cudaSetDevice(device));
-        if (const char* v = std::getenv("VMCUDA_CHUNK_FRAMES")) e->chunk_frames = std::max(1, std::atoi(v));
-        if (const char* v = std::getenv("VMCUDA_CHUNK_CANDIDATES")) e->chunk_candidates = std::max<long long>(1, std::atoll(v));
+        if (const char* v = std::getenv("VMCUDA_CHUNK_FRAMES")) {
+            e->chunk_frames   = std::max(1, std::atoi(v));
+            e->chunk_override = true;
+        }
+        if (const char* v = std::getenv("VMCUDA_CHUNK_CANDIDATES")) {
+            e->chunk_candidates = std::max<long long>(1, std::atoll(v));
+            e->chunk_override   = true;
+        }
         if (const char* v = std::getenv("VMCUDA_TC")) {
             e->tc_mode = std::atoi(v);
             e->use_tc  = e->tc_mode != 0;
