@@ -231,14 +231,13 @@ static void launch_conv_t(const ConvArgs& a, dim3 grid_rows, int max_rows, cudaS
 
 constexpr int CW_MAX = 2320;  // floats: a 16 -> 16 layer with 8 neighbours and its biases
 
-template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS, int NSLOTS = 0>
+template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS>
 static bool launch_conv_cw(const DenseLayer& L, const ConvArgs& a, dim3 grid_rows, int max_rows, cudaStream_t s) {
     if (L.host_packed.size() > static_cast<size_t>(WMAX)) return false;
-    if (NSLOTS > 0 && L.n_slots != NSLOTS) return false;
     ConvWeights<WMAX> wp;
     std::memcpy(wp.w, L.host_packed.data(), L.host_packed.size() * sizeof(float));
     dim3 grid((max_rows + T * R - 1) / (T * R), grid_rows.y);
-    k_graph_conv_cw<CIN, COUT, R, WMAX, T, NSLOTS><<<grid, T, 0, s>>>(a, wp);
+    k_graph_conv_cw<CIN, COUT, R, WMAX, T><<<grid, T, 0, s>>>(a, wp);
     return true;
 }
 
@@ -252,7 +251,7 @@ static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, 
         const char* v = std::getenv("VMCUDA_CONST_WEIGHTS");
         return v == nullptr || v[0] != '0';
     }();
-    // the 16 -> 16 layer measured best with two rows per thread and 256 threads (103 us against 111 us per 1.1 M rows)
+    // the 16 -> 16 layer measured best with two rows per thread and 256 threads
     if (const_weights && L.cin == 16 && L.cout == 16 && launch_conv_cw<16, 16, 2, CW_MAX, 256>(L, a, grid, max_rows, s)) return true;
 #define VM_CONV(CI, CO, RR)                                                                       \
     if (L.cin == CI && L.cout == CO) {                                                            \

@@ -473,7 +473,23 @@ struct ConvWeights {
     float w[WMAX];
 };
 
-template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS, int NSLOTS = 0>
+// Packed single-precision FMA of sm_100 (two independent IEEE fused multiply-adds per instruction): halves the
+// number of FMA instructions of a kernel that is bound by instruction issue, not by the FMA pipe.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void ffma2(unsigned long long& acc, unsigned long long a, unsigned long long b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+
+// Accumulators live as pairs of adjacent output columns, each weight pair is one 64-bit constant load shared by the R
+// rows, each input value is duplicated into a pair once per row and k.
+template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS>
 __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __grid_constant__ ConvWeights<WMAX> wp) {
     static_assert(CIN % 4 == 0, "vector loads of the input rows");
     constexpr int COUTP = (COUT + 3) & ~3;
@@ -483,23 +499,20 @@ __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __g
     const int rows           = a.offsets[frame + 1] - start + 1;
     const int first          = blockIdx.x * (T * R);
     if (first >= rows) return;
-    // NSLOTS > 0: the slot loop is unrolled and every weight is an immediate constant-bank operand of its FFMA
-    const int n_slots     = NSLOTS > 0 ? NSLOTS : a.n_slots;
-    const int K           = n_slots * CIN;
+    const int K           = a.n_slots * CIN;
     const int local_base  = start - a.offsets[a.f0] + frame_in_chunk;
     const size_t nb_base  = static_cast<size_t>(start + frame);
 
     int row[R];
-    float acc[R][COUTP];
+    unsigned long long acc[R][COUTP / 2];
 #pragma unroll
     for (int q = 0; q < R; ++q) {
         row[q] = min(first + q * T + static_cast<int>(threadIdx.x), rows - 1);
 #pragma unroll
-        for (int j = 0; j < COUTP; ++j) acc[q][j] = wp.w[K * COUTP + j];
+        for (int j = 0; j < COUTP / 2; ++j) acc[q][j] = pack2(wp.w[K * COUTP + 2 * j], wp.w[K * COUTP + 2 * j + 1]);
     }
     const float4* in4 = reinterpret_cast<const float4*>(a.in);
-#pragma unroll(NSLOTS > 0 ? NSLOTS : 1)
-    for (int s = 0; s < n_slots; ++s) {
+    for (int s = 0; s < a.n_slots; ++s) {
         int src_row[R];
 #pragma unroll
         for (int q = 0; q < R; ++q) {
@@ -514,14 +527,18 @@ __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __g
             for (int q = 0; q < R; ++q) x[q] = in4[static_cast<size_t>(c4) * a.in_stride + src_row[q]];
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
+                unsigned long long xx[R];
 #pragma unroll
-                for (int j = 0; j < COUTP; ++j) {
-                    const float w = wp.w[w_slot + (c4 * 4 + kk) * COUTP + j];
+                for (int q = 0; q < R; ++q) {
+                    const float xv = kk == 0 ? x[q].x : kk == 1 ? x[q].y : kk == 2 ? x[q].z : x[q].w;
+                    xx[q]          = pack2(xv, xv);
+                }
 #pragma unroll
-                    for (int q = 0; q < R; ++q) {
-                        const float xv = kk == 0 ? x[q].x : kk == 1 ? x[q].y : kk == 2 ? x[q].z : x[q].w;
-                        acc[q][j]      = fmaf(xv, w, acc[q][j]);
-                    }
+                for (int j = 0; j < COUTP / 2; ++j) {
+                    const int at               = w_slot + (c4 * 4 + kk) * COUTP + 2 * j;
+                    const unsigned long long w = pack2(wp.w[at], wp.w[at + 1]);
+#pragma unroll
+                    for (int q = 0; q < R; ++q) ffma2(acc[q][j], xx[q], w);
                 }
             }
         }
@@ -531,26 +548,27 @@ __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __g
     for (int q = 0; q < R; ++q) {
         const int i = first + q * T + static_cast<int>(threadIdx.x);
         if (i >= rows) continue;
-        activate<COUT>(acc[q], a.activation);
+        float v[COUTP];
+#pragma unroll
+        for (int j = 0; j < COUTP / 2; ++j) unpack2(acc[q][j], v[2 * j], v[2 * j + 1]);
+        activate<COUT>(v, a.activation);
         float* dst = a.out + (out_base + i) * COUT;
         if (COUT % 4 == 0 && a.out_planar) {
             float4* out4 = reinterpret_cast<float4*>(a.out);
 #pragma unroll
             for (int j4 = 0; j4 < COUT / 4; ++j4) {
-                out4[static_cast<size_t>(j4) * a.out_stride + out_base + i] =
-                  make_float4(acc[q][j4 * 4], acc[q][j4 * 4 + 1], acc[q][j4 * 4 + 2], acc[q][j4 * 4 + 3]);
+                out4[static_cast<size_t>(j4) * a.out_stride + out_base + i] = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
             }
         }
         else if (COUT % 4 == 0) {
 #pragma unroll
             for (int j4 = 0; j4 < COUT / 4; ++j4) {
-                *reinterpret_cast<float4*>(dst + j4 * 4) =
-                  make_float4(acc[q][j4 * 4], acc[q][j4 * 4 + 1], acc[q][j4 * 4 + 2], acc[q][j4 * 4 + 3]);
+                *reinterpret_cast<float4*>(dst + j4 * 4) = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
             }
         }
         else {
 #pragma unroll
-            for (int j = 0; j < COUT; ++j) dst[j] = acc[q][j];
+            for (int j = 0; j < COUT; ++j) dst[j] = v[j];
         }
     }
 }
