@@ -37,7 +37,7 @@ from visualmesh_b200 import workloads as W  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture summarised in
 # profiles/ (None until captured); scaled to the launch's rows when the capture ran a smaller case.
-NCU_TRAFFIC_BYTES_PER_ROW = 119.4  # profiles/graph_conv_16x16_cfg1_16frames.md: 132.4 MB over 1,108,261 rows
+NCU_TRAFFIC_BYTES_PER_ROW = 119.2  # profiles/graph_conv_16x16_cfg1_16frames.md: 132.1 MB over 1,108,261 rows
 
 
 def _peaks():
