@@ -271,7 +271,7 @@ static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, 
 
 template <int CIN, int NP, int NSLOTS, bool HALF>
 static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
-    constexpr int STAGES = 3;
+    constexpr int STAGES = CIN >= 32 ? 2 : 3;  // 32-channel stages are 16 KB: two of them leave room for a third CTA per SM
     const size_t smem    = tc::smem_bytes<CIN, NP, STAGES, HALF>(NSLOTS);
     static int ctas_per_sm = 0;
     static int n_sms       = 0;
