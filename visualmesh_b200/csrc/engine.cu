@@ -255,7 +255,8 @@ static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, 
     if (const_weights && L.cin == 16 && L.cout == 16 && launch_conv_cw<16, 16, 2, CW_MAX, 256>(L, a, grid, max_rows, s)) return true;
 #define VM_CONV(CI, CO, RR)                                                                       \
     if (L.cin == CI && L.cout == CO) {                                                            \
-        if (const_weights && launch_conv_cw<CI, CO, RR, CW_MAX>(L, a, grid, max_rows, s)) return true; \
+        /* 4-channel first layers are gather-bound and measured faster with the weights in shared memory */ \
+        if (const_weights && CI > 4 && launch_conv_cw<CI, CO, RR, CW_MAX>(L, a, grid, max_rows, s)) return true; \
         launch_conv_t<CI, CO, RR>(a, grid, max_rows, s);                                          \
         return true;                                                                              \
     }
