@@ -86,7 +86,7 @@ namespace tc {
         int32_t* abort_flag;
     };
 
-    constexpr int ABORT_TC_RANGE = 3;  // a feature value too large for the fp16 split: the host falls back to FFMA
+    constexpr int ABORT_TC_RANGE = ABORT_RANGE;  // a feature value too large for the fp16 split: the host falls back to FFMA
 
     // Element formats of the split. HALF: x = h + l with h, l fp16 (kind::f16, 8 channels per 16-byte chunk, K = 16
     // per MMA) - half the shared-memory traffic of the fp32 container formats, needs |x| < 65504. Otherwise TF32:
@@ -402,7 +402,8 @@ namespace tc {
                                                              : tanhf(v[j]);
                         }
                     }
-                    if (a.out_planar) {
+                    if (a.out_split && t.cout == NP) { store_split<NP>(a.out, a.out_stride, out_row, v, a.range_flag); }
+                    else if (a.out_planar) {
                         float4* out4 = reinterpret_cast<float4*>(a.out);
 #pragma unroll
                         for (int j4 = 0; j4 < NP / 4; ++j4) {
@@ -432,6 +433,283 @@ namespace tc {
                 atomicCAS(t.abort_flag, 0, ABORT_TC_RANGE);
             }
         }
+        if (warp == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        }
+    }
+
+    // ---- the same layer fed from the split feature layout ---------------------------------------------------------
+    // When the producing layer has already stored its output as fp16 hi/lo planes (store_split), assembling the A tile
+    // is a pure copy: each gather thread issues 16-byte cp.async copies from the neighbour's planes straight into the
+    // stage (the planes have the UMMA chunk shape), several slots ahead, with no registers and no arithmetic in between.
+    __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    }
+    __device__ __forceinline__ void cp_async_commit() {
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    template <int N>
+    __device__ __forceinline__ void cp_async_wait() {
+        asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+    }
+
+    template <int CIN, int NP, int STAGES>
+    constexpr size_t smem_bytes_split(int n_slots) {
+        return 256 + static_cast<size_t>(STAGES) * 2 * (CIN / 8) * TILE_ROWS * 16 + static_cast<size_t>(n_slots) * (CIN / 8) * 2 * NP * 16;
+    }
+
+    template <int CIN, int NP, int STAGES, int NSLOTS>
+    __global__ void __launch_bounds__(CTA_THREADS) k_graph_conv_tc_split(const ConvArgs a, const Args t) {
+        static_assert(NP == 16 || NP == 32, "unsupported tile width");
+        static_assert(CIN % 16 == 0, "a slot must hold whole K steps of 16 fp16 channels");
+        constexpr int PLANES     = CIN / 8;
+        constexpr int PLANE      = TILE_ROWS * 16;
+        constexpr int SLOT_BYTES = PLANES * PLANE;
+        constexpr int WCHUNK     = 2 * NP * 16;
+        constexpr int TMEM_COLS  = 4 * NP;
+        constexpr int AHEAD      = STAGES - 1 < NSLOTS ? STAGES - 1 : NSLOTS;  // slots in flight ahead of the one handed over
+
+        extern __shared__ __align__(1024) unsigned char smem_raw[];
+        __shared__ uint64_t bars[2 * STAGES + 4];
+        __shared__ uint32_t tmem_base_slot;
+        __shared__ int32_t tile_prefix[MAX_FRAMES + 1];
+        __shared__ int32_t failed_s;
+        volatile int32_t* failed = &failed_s;
+
+        const int tid  = threadIdx.x;
+        const int warp = tid >> 5;
+        const int lane = tid & 31;
+        unsigned char* stage_base = smem_raw;
+        unsigned char* w_s        = smem_raw + static_cast<size_t>(STAGES) * 2 * SLOT_BYTES;
+        const uint32_t bar_full      = smem_u32(&bars[0]);
+        const uint32_t bar_empty     = smem_u32(&bars[STAGES]);
+        const uint32_t bar_acc_full  = smem_u32(&bars[2 * STAGES]);
+        const uint32_t bar_acc_empty = smem_u32(&bars[2 * STAGES + 2]);
+
+        if (tid == 0) {
+            failed_s = 0;
+            for (int i = 0; i < STAGES; ++i) {
+                mbar_init(bar_full + 8 * i, PRODUCER_WARPS);
+                mbar_init(bar_empty + 8 * i, 1);
+            }
+            for (int i = 0; i < 2; ++i) {
+                mbar_init(bar_acc_full + 8 * i, 1);
+                mbar_init(bar_acc_empty + 8 * i, PRODUCER_WARPS);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            int run = 0;
+            for (int f = 0; f < t.n_frames; ++f) {
+                tile_prefix[f] = run;
+                const int rows = a.offsets[a.f0 + f + 1] - a.offsets[a.f0 + f] + 1;
+                run += (rows + TILE_ROWS - 1) / TILE_ROWS;
+            }
+            tile_prefix[t.n_frames] = run;
+        }
+        if (warp == 0) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        {
+            const uint4* g = reinterpret_cast<const uint4*>(t.w_cat);
+            uint4* sw      = reinterpret_cast<uint4*>(w_s);
+            for (int i = tid; i < NSLOTS * PLANES * 2 * NP; i += CTA_THREADS) sw[i] = __ldg(g + i);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_base = tmem_base_slot;
+        const int total_tiles    = tile_prefix[t.n_frames];
+
+        if (warp == PRODUCER_WARPS) {
+            // ================= MMA issuer =================
+            if (lane == 0) {
+                constexpr uint32_t IDESC_BASE = (1u << 4) | (static_cast<uint32_t>(TILE_ROWS >> 4) << 24);  // fp16 x fp16 -> fp32, K-major
+                constexpr uint32_t IDESC_CAT  = IDESC_BASE | (static_cast<uint32_t>((2 * NP) >> 3) << 17);
+                constexpr uint32_t IDESC_HI   = IDESC_BASE | (static_cast<uint32_t>(NP >> 3) << 17);
+                const uint32_t w_addr = smem_u32(w_s);
+                const uint32_t a_addr = smem_u32(stage_base);
+                uint32_t it = 0, tile_count = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
+                    const uint32_t ab  = tile_count & 1u;
+                    const uint32_t acc = tmem_base + ab * (2 * NP);
+                    if (tile_count >= 2 && !mbar_wait_or_fail(bar_acc_empty + 8 * ab, ((tile_count >> 1) - 1) & 1u, failed)) {
+                        ok = false;
+                        break;
+                    }
+                    for (int s = 0; s < NSLOTS; ++s, ++it) {
+                        const uint32_t stage = it % STAGES;
+                        const uint32_t use   = it / STAGES;
+                        if (!mbar_wait_or_fail(bar_full + 8 * stage, use & 1u, failed)) {
+                            ok = false;
+                            break;
+                        }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t a_hi = a_addr + stage * 2 * SLOT_BYTES;
+                        const uint32_t a_lo = a_hi + SLOT_BYTES;
+#pragma unroll
+                        for (int ks = 0; ks < PLANES / 2; ++ks) {
+                            const uint64_t da_hi = smem_desc(a_hi + ks * 2 * PLANE, PLANE, 128);
+                            const uint64_t da_lo = smem_desc(a_lo + ks * 2 * PLANE, PLANE, 128);
+                            const uint64_t db    = smem_desc(w_addr + (s * PLANES + ks * 2) * WCHUNK, WCHUNK, 128);
+                            mma<true>(acc, da_hi, db, IDESC_CAT, (s == 0 && ks == 0) ? 0u : 1u);
+                            mma<true>(acc, da_lo, db, IDESC_HI, 1u);
+                        }
+                        commit(bar_empty + 8 * stage);
+                        if (s == NSLOTS - 1) commit(bar_acc_full + 8 * ab);
+                    }
+                }
+                if (!ok) failed_s = 1;
+            }
+        }
+        else {
+            // ================= copy issuers + epilogue =================
+            const unsigned char* in_b = reinterpret_cast<const unsigned char*>(a.in);
+            const uint32_t a_addr     = smem_u32(stage_base);
+            uint32_t tile_count = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
+                int f = 0;
+                while (f + 1 < t.n_frames && tile_prefix[f + 1] <= tile) ++f;
+                const int frame      = a.f0 + f;
+                const int start      = a.offsets[frame];
+                const int rows       = a.offsets[frame + 1] - start + 1;
+                const int row        = (tile - tile_prefix[f]) * TILE_ROWS + tid;
+                const int rowc       = min(row, rows - 1);
+                const int local_base = start - a.offsets[a.f0] + f;
+                const size_t nb_base = static_cast<size_t>(start + frame);
+                const uint32_t ab    = tile_count & 1u;
+                const uint32_t acc   = tmem_base + ab * (2 * NP);
+                const uint32_t it0   = tile_count * NSLOTS;
+
+                int src_rows[NSLOTS];
+                src_rows[0] = local_base + rowc;
+#pragma unroll
+                for (int s = 1; s < NSLOTS; ++s) src_rows[s] = local_base + __ldg(a.nb + (nb_base + rowc) * a.n_neighbours + (s - 1));
+
+                // issue the copies of slot s into its stage (after the MMAs of the stage's previous use have read it)
+                auto issue = [&](int s) {
+                    const uint32_t it    = it0 + s;
+                    const uint32_t stage = it % STAGES;
+                    const uint32_t use   = it / STAGES;
+                    if (use > 0 && !mbar_wait_or_fail(bar_empty + 8 * stage, (use - 1) & 1u, failed)) ok = false;
+                    const uint32_t hi = a_addr + stage * 2 * SLOT_BYTES + tid * 16;
+                    const uint32_t lo = hi + SLOT_BYTES;
+#pragma unroll
+                    for (int p = 0; p < PLANES; ++p) {
+                        cp_async16(hi + p * PLANE, in_b + (static_cast<size_t>(p) * a.in_stride + src_rows[s]) * 16);
+                        cp_async16(lo + p * PLANE, in_b + (static_cast<size_t>(PLANES + p) * a.in_stride + src_rows[s]) * 16);
+                    }
+                    cp_async_commit();
+                };
+#pragma unroll
+                for (int s = 0; s < AHEAD; ++s) issue(s);
+#pragma unroll
+                for (int s = 0; s < NSLOTS; ++s) {
+                    if (s + AHEAD < NSLOTS) {
+                        issue(s + AHEAD);
+                        cp_async_wait<AHEAD>();  // everything but the AHEAD newest groups has landed: slot s is in
+                    }
+                    else {
+                        // no newer group was issued: groups still allowed in flight = slots after s
+                        switch (NSLOTS - 1 - s) {
+                            case 0: cp_async_wait<0>(); break;
+                            case 1: cp_async_wait<1>(); break;
+                            case 2: cp_async_wait<2>(); break;
+                            case 3: cp_async_wait<3>(); break;
+                            case 4: cp_async_wait<4>(); break;
+                            case 5: cp_async_wait<5>(); break;
+                            case 6: cp_async_wait<6>(); break;
+                            default: cp_async_wait<7>(); break;
+                        }
+                    }
+                    // this thread's copies of slot s are in shared memory: publish them to the tensor core
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * ((it0 + s) % STAGES));
+                }
+                ok = __all_sync(0xffffffffu, ok) && !*failed;
+                if (!ok) break;
+
+                const bool arrived = mbar_wait_or_fail(bar_acc_full + 8 * ab, (tile_count >> 1) & 1u, failed);
+                ok                 = __all_sync(0xffffffffu, arrived);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                float v[NP];
+#pragma unroll
+                for (int j0 = 0; j0 < 2 * NP; j0 += 16) {
+                    uint32_t r[16];
+                    const uint32_t taddr = acc + (static_cast<uint32_t>(warp * 32) << 16) + j0;
+                    asm volatile(
+                      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                      : "r"(taddr));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j0 < NP) { v[j0 + j] = __uint_as_float(r[j]); }
+                        else {
+                            v[j0 + j - NP] = v[j0 + j - NP] + __uint_as_float(r[j]);
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_acc_empty + 8 * ab);
+#pragma unroll
+                for (int j = 0; j < NP; ++j) v[j] = v[j] + __ldg(t.bias + j);
+                if (row < rows) {
+                    const size_t out_row = (a.out_global ? nb_base : static_cast<size_t>(local_base)) + row;
+                    if (a.activation == VM_SOFTMAX) {
+                        float total = 0.0f;
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            if (j < t.cout) {
+                                v[j]  = expf(v[j]);
+                                total = __fadd_rn(total, v[j]);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) v[j] = __fdiv_rn(v[j], total);
+                    }
+                    else {
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            v[j] = a.activation == VM_SELU ? selu(v[j])
+                                   : a.activation == VM_RELU ? ((v[j] < 0.0f) ? 0.0f : v[j])
+                                                             : tanhf(v[j]);
+                        }
+                    }
+                    if (a.out_split && t.cout == NP) { store_split<NP>(a.out, a.out_stride, out_row, v, a.range_flag); }
+                    else if (a.out_planar) {
+                        float4* out4 = reinterpret_cast<float4*>(a.out);
+#pragma unroll
+                        for (int j4 = 0; j4 < NP / 4; ++j4) {
+                            if (j4 * 4 < t.cout) {
+                                out4[static_cast<size_t>(j4) * a.out_stride + out_row] = make_float4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+                            }
+                        }
+                    }
+                    else {
+                        float* dst = a.out + out_row * t.cout;
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            if (j < t.cout) dst[j] = v[j];
+                        }
+                    }
+                }
+            }
+            if (!ok && lane == 0) failed_s = 1;
+            cp_async_wait<0>();
+        }
+
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (tid == 0 && failed_s) atomicExch(t.abort_flag, ABORT_TC_TIMEOUT);
         if (warp == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");

@@ -191,6 +191,8 @@ struct vm_engine {
     int64_t launches = 0;
     bool use_tc      = true;
     int tc_mode      = 1;
+    int tc_min_product = 512;   // mode 1: layers with C_in x C_out at least this run on the tensor cores
+    bool tc_no_split = false;   // debugging: never use the split feature layout
     cudaEvent_t ev_timer_start = nullptr, ev_timer_stop = nullptr;
 };
 
@@ -215,6 +217,21 @@ static void end_stage(vm_engine* e, cudaStream_t s) {
 }
 
 // ---- graph convolution dispatch ----------------------------------------------------------------------------------
+
+// layer shapes (C_in, C_out, rows per thread) with a specialised FFMA kernel
+#define VM_CONV_SHAPES(X)                                                                                   \
+    X(4, 2, 4) X(4, 3, 4) X(4, 4, 4) X(4, 8, 4) X(4, 12, 4) X(4, 16, 4) X(4, 32, 2)                         \
+    X(8, 2, 4) X(8, 3, 4) X(8, 4, 4) X(8, 5, 4) X(8, 8, 4) X(8, 12, 4) X(8, 16, 4)                          \
+    X(12, 2, 4) X(12, 3, 4) X(12, 4, 4) X(12, 8, 4) X(12, 12, 4) X(12, 16, 4)                               \
+    X(16, 2, 4) X(16, 3, 4) X(16, 4, 4) X(16, 5, 4) X(16, 8, 4) X(16, 12, 4) X(16, 16, 4) X(16, 32, 2)      \
+    X(32, 2, 4) X(32, 3, 4) X(32, 4, 4) X(32, 8, 4) X(32, 16, 4) X(32, 32, 2)
+
+static bool has_fast_ffma_kernel(int cin, int cout) {
+#define VM_IS(CI, CO, RR) if (cin == CI && cout == CO) return true;
+    VM_CONV_SHAPES(VM_IS)
+#undef VM_IS
+    return false;
+}
 
 template <int CIN, int COUT, int R, int T = CONV_THREADS, int MINB = 1>
 static void launch_conv_t(const ConvArgs& a, dim3 grid_rows, int max_rows, cudaStream_t s) {
@@ -260,12 +277,7 @@ static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, 
         launch_conv_t<CI, CO, RR>(a, grid, max_rows, s);                                          \
         return true;                                                                              \
     }
-    VM_CONV(4, 2, 4) VM_CONV(4, 3, 4) VM_CONV(4, 4, 4) VM_CONV(4, 8, 4) VM_CONV(4, 12, 4) VM_CONV(4, 16, 4) VM_CONV(4, 32, 2)
-    VM_CONV(8, 2, 4) VM_CONV(8, 3, 4) VM_CONV(8, 4, 4) VM_CONV(8, 5, 4) VM_CONV(8, 8, 4) VM_CONV(8, 12, 4) VM_CONV(8, 16, 4)
-    VM_CONV(12, 2, 4) VM_CONV(12, 3, 4) VM_CONV(12, 4, 4) VM_CONV(12, 8, 4) VM_CONV(12, 12, 4) VM_CONV(12, 16, 4)
-    VM_CONV(16, 2, 4) VM_CONV(16, 3, 4) VM_CONV(16, 4, 4) VM_CONV(16, 5, 4) VM_CONV(16, 8, 4) VM_CONV(16, 12, 4) VM_CONV(16, 16, 4)
-    VM_CONV(16, 32, 2)
-    VM_CONV(32, 2, 4) VM_CONV(32, 3, 4) VM_CONV(32, 4, 4) VM_CONV(32, 8, 4) VM_CONV(32, 16, 4) VM_CONV(32, 32, 2)
+    VM_CONV_SHAPES(VM_CONV)
 #undef VM_CONV
     return false;
 }
@@ -301,11 +313,56 @@ static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frame
     tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
 }
 
+template <int CIN, int NP, int NSLOTS>
+static void launch_conv_tc_split_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
+    constexpr int STAGES = CIN >= 32 ? 3 : 4;
+    const size_t smem    = tc::smem_bytes_split<CIN, NP, STAGES>(NSLOTS);
+    static int ctas_per_sm = 0;
+    static int n_sms       = 0;
+    if (ctas_per_sm == 0) {
+        VM_CUDA(cudaFuncSetAttribute(tc::k_graph_conv_tc_split<CIN, NP, STAGES, NSLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        int dev = 0;
+        VM_CUDA(cudaGetDevice(&dev));
+        VM_CUDA(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
+        const int by_smem = static_cast<int>((220 * 1024) / (smem + 2048));
+        const int by_tmem = 512 / (4 * NP);
+        cudaFuncAttributes attr;
+        VM_CUDA(cudaFuncGetAttributes(&attr, tc::k_graph_conv_tc_split<CIN, NP, STAGES, NSLOTS>));
+        const int regs_per_cta = ((attr.numRegs + 7) / 8 * 8) * tc::CTA_THREADS;
+        const int by_regs      = 65536 / std::max(1, regs_per_cta);
+        ctas_per_sm            = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
+        if (const char* v = std::getenv("VMCUDA_TC_CTAS")) ctas_per_sm = std::max(1, std::atoi(v));
+    }
+    tc::Args t{};
+    t.w_cat      = L.d_tc_cat;
+    t.bias       = L.d_tc_bias;
+    t.n_frames   = n_frames;
+    t.cout       = L.cout;
+    t.abort_flag = abort_flag;
+    const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
+    const int grid        = std::max(1, std::min(tiles_upper, n_sms * ctas_per_sm));
+    tc::k_graph_conv_tc_split<CIN, NP, STAGES, NSLOTS><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
+}
+
+// The tensor-core kernel fed from the split feature layout exists for these shapes.
+static bool has_tc_split_kernel(const DenseLayer& L) {
+    return L.tc_np != 0 && L.tc_half && (L.cin == 16 || L.cin == 32) && (L.n_slots == 5 || L.n_slots == 7 || L.n_slots == 9);
+}
+
+static bool launch_conv_tc_split(vm_engine* e, const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, cudaStream_t s) {
+#define VM_TCS(CI, NPAD, NS)                                                              \
+    if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS) {                               \
+        launch_conv_tc_split_t<CI, NPAD, NS>(L, a, n_frames, max_rows, e->d_abort, s);     \
+        return true;                                                                       \
+    }
+    VM_TCS(16, 16, 5) VM_TCS(16, 16, 7) VM_TCS(16, 16, 9) VM_TCS(16, 32, 5) VM_TCS(16, 32, 7) VM_TCS(16, 32, 9)
+    VM_TCS(32, 16, 5) VM_TCS(32, 16, 7) VM_TCS(32, 16, 9) VM_TCS(32, 32, 5) VM_TCS(32, 32, 7) VM_TCS(32, 32, 9)
+#undef VM_TCS
+    return false;
+}
+
 static bool launch_conv_tc(vm_engine* e, const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, cudaStream_t s) {
     if (L.tc_np == 0 || n_frames > tc::MAX_FRAMES) return false;
-    // mode 1 (default): only where the contraction is dense enough to pay - measured: 32-wide layers 1.7x faster than
-    // the FFMA kernel, 16 x 16 a tie, narrower layers slower; mode 2: wherever a tensor-core kernel exists
-    if (e->tc_mode == 1 && L.cin * L.cout < 512) return false;
 #define VM_TC(CI, NPAD, NS, HF)                                                      \
     if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS && L.tc_half == HF) {        \
         launch_conv_tc_t<CI, NPAD, NS, HF>(L, a, n_frames, max_rows, e->d_abort, s);   \
@@ -320,14 +377,17 @@ static bool launch_conv_tc(vm_engine* e, const DenseLayer& L, const ConvArgs& a,
     return false;
 }
 
-static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_frames, int max_rows, cudaStream_t s) {
+enum ConvKind { CONV_FFMA = 0, CONV_TC_GATHER = 1, CONV_TC_SPLIT = 2 };
+
+static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_frames, int max_rows, cudaStream_t s, ConvKind kind) {
     a.weights     = L.d_weights;
     a.biases      = L.d_weights + static_cast<size_t>(L.n_slots) * L.cin * L.coutp;
     a.n_slots     = L.n_slots;
     a.activation  = L.activation;
     dim3 grid(1, n_frames);
     begin_stage(e, s, L.stage.c_str());
-    if (e->use_tc && launch_conv_tc(e, L, a, n_frames, max_rows, s)) {}
+    if (kind == CONV_TC_SPLIT && launch_conv_tc_split(e, L, a, n_frames, max_rows, s)) {}
+    else if (kind == CONV_TC_GATHER && launch_conv_tc(e, L, a, n_frames, max_rows, s)) {}
     else if (!launch_conv_fast(L, a, grid, max_rows, s)) {
         dim3 g((max_rows + CONV_THREADS - 1) / CONV_THREADS, n_frames);
         k_graph_conv_generic<<<g, CONV_THREADS, 0, s>>>(a, L.cin, L.cout, L.coutp);
@@ -348,9 +408,23 @@ static void run_network(vm_engine* e,
                         float* out_final,
                         bool final_global,
                         int feature_stride) {
+    // Which kernel runs each layer. Tensor cores where the contraction is dense enough to pay (mode 1, the default:
+    // C_in x C_out >= 512), wherever a kernel exists (mode 2), never (mode 0). A tensor-core layer whose producer can
+    // write the split layout is fed by plain copies (CONV_TC_SPLIT); otherwise it gathers and splits fp32 itself.
+    const size_t n_layers = e->layers.size();
+    std::vector<ConvKind> kind(n_layers, CONV_FFMA);
+    for (size_t l = 0; l < n_layers; ++l) {
+        const DenseLayer& L = e->layers[l];
+        if (!e->use_tc || L.tc_np == 0 || n_frames > tc::MAX_FRAMES) continue;
+        if (e->tc_mode == 1 && L.cin * L.cout < e->tc_min_product) continue;
+        const bool producer_can_split =
+          l > 0 && L.n_slots > 1 && (kind[l - 1] != CONV_FFMA || has_fast_ffma_kernel(e->layers[l - 1].cin, e->layers[l - 1].cout));
+        kind[l] = (has_tc_split_kernel(L) && producer_can_split && !e->tc_no_split) ? CONV_TC_SPLIT : CONV_TC_GATHER;
+        if (kind[l] == CONV_TC_GATHER && L.n_slots == 1) kind[l] = CONV_FFMA;  // dense-only layers have no tensor-core kernel
+    }
     int cur = 0;
-    for (size_t l = 0; l < e->layers.size(); ++l) {
-        const bool last = l + 1 == e->layers.size();
+    for (size_t l = 0; l < n_layers; ++l) {
+        const bool last = l + 1 == n_layers;
         ConvArgs a{};
         a.in           = lane.d_feat[cur].p;
         a.out          = last ? out_final : lane.d_feat[cur ^ 1].p;
@@ -362,7 +436,9 @@ static void run_network(vm_engine* e,
         a.in_stride    = feature_stride;
         a.out_stride   = feature_stride;
         a.out_planar   = (!last && e->layers[l].cout % 4 == 0) ? 1 : 0;
-        launch_conv(e, e->layers[l], a, n_frames, max_rows, lane.stream);
+        a.out_split    = (!last && kind[l + 1] == CONV_TC_SPLIT) ? 1 : 0;
+        a.range_flag   = e->d_abort;
+        launch_conv(e, e->layers[l], a, n_frames, max_rows, lane.stream, kind[l]);
         cur ^= 1;
     }
 }
@@ -827,6 +903,8 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
             e->tc_mode = std::atoi(v);
             e->use_tc  = e->tc_mode != 0;
         }
+        if (const char* v = std::getenv("VMCUDA_TC_MIN_PRODUCT")) e->tc_min_product = std::atoi(v);
+        if (const char* v = std::getenv("VMCUDA_TC_NO_SPLIT")) e->tc_no_split = std::atoi(v) != 0;
         if (const char* v = std::getenv("VMCUDA_LANES")) e->n_lanes = std::min(MAX_LANES, std::max(1, std::atoi(v)));
         for (int l = 0; l < MAX_LANES; ++l) {
             Lane& lane = e->lanes[l];

@@ -10,6 +10,7 @@
 // offsets[f] - offsets[f0] + (f - f0) where f0 is the chunk's first frame.
 #pragma once
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "device_math.cuh"
@@ -341,7 +342,42 @@ struct ConvArgs {
     int32_t in_stride;      // rows per planar chunk of `in`
     int32_t out_stride;     // rows per planar chunk of `out`
     int32_t out_planar;     // write `out` chunk-planar (needs COUT % 4 == 0 and !out_global)
+    int32_t out_split;      // write `out` as fp16 hi/lo planes for a tensor-core consumer (needs COUT % 8 == 0)
+    int32_t* range_flag;    // raised (to 3) when a value is too large for the fp16 split
 };
+
+// The "split" feature layout, produced for a layer that runs on the tensor cores. Every fp32 value x is stored as two
+// fp16 values, hi = fp16(x) and lo = fp16(x - hi) (x = hi + lo to ~2^-22 relative, absolute error <= 3e-8 for small
+// x), in the shape the tensor-core kernel copies straight into shared memory: 16-byte chunks of 8 channels, chunk
+// plane p of row r at byte ((p * stride + r) * 16), the C/8 hi planes first, then the C/8 lo planes. Same footprint as
+// fp32. Values beyond the fp16 range raise the range flag; the host then recomputes without the tensor-core path.
+constexpr int ABORT_RANGE = 3;
+
+template <int COUT>
+__device__ __forceinline__ void store_split(float* out, int stride, size_t row, const float* v, int32_t* range_flag) {
+    static_assert(COUT % 8 == 0, "split layout needs whole 8-channel chunks");
+    constexpr int P = COUT / 8;
+    unsigned char* base = reinterpret_cast<unsigned char*>(out);
+    bool bad            = false;
+#pragma unroll
+    for (int p = 0; p < P; ++p) {
+        uint32_t h[4], l[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const float x0 = v[8 * p + 2 * q], x1 = v[8 * p + 2 * q + 1];
+            bad |= fabsf(x0) > 60000.0f || fabsf(x1) > 60000.0f;
+            const __half h0 = __float2half_rn(x0);
+            const __half h1 = __float2half_rn(x1);
+            const __half l0 = __float2half_rn(x0 - __half2float(h0));
+            const __half l1 = __float2half_rn(x1 - __half2float(h1));
+            h[q] = static_cast<uint32_t>(__half_as_ushort(h0)) | (static_cast<uint32_t>(__half_as_ushort(h1)) << 16);
+            l[q] = static_cast<uint32_t>(__half_as_ushort(l0)) | (static_cast<uint32_t>(__half_as_ushort(l1)) << 16);
+        }
+        *reinterpret_cast<uint4*>(base + (static_cast<size_t>(p) * stride + row) * 16)     = make_uint4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<uint4*>(base + (static_cast<size_t>(P + p) * stride + row) * 16) = make_uint4(l[0], l[1], l[2], l[3]);
+    }
+    if (bad) atomicCAS(range_flag, 0, ABORT_RANGE);
+}
 
 // Each thread owns R rows strided by the block size, so a warp's loads and stores of one row index are contiguous.
 // The layer's weights sit in shared memory; every weight read is a 128-bit broadcast shared by the R rows.
@@ -443,7 +479,8 @@ __global__ void __launch_bounds__(T, MINB) k_graph_conv(const ConvArgs a) {
         if (i >= rows) continue;
         activate<COUT>(acc[q], a.activation);
         float* dst = a.out + (out_base + i) * COUT;
-        if (COUT % 4 == 0 && a.out_planar) {
+        if (COUT % 8 == 0 && a.out_split) { store_split<(COUT % 8 == 0 ? COUT : 8)>(a.out, a.out_stride, out_base + i, acc[q], a.range_flag); }
+        else if (COUT % 4 == 0 && a.out_planar) {
             float4* out4 = reinterpret_cast<float4*>(a.out);
 #pragma unroll
             for (int j4 = 0; j4 < COUT / 4; ++j4) {
@@ -553,7 +590,8 @@ __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __g
         for (int j = 0; j < COUTP / 2; ++j) unpack2(acc[q][j], v[2 * j], v[2 * j + 1]);
         activate<COUT>(v, a.activation);
         float* dst = a.out + (out_base + i) * COUT;
-        if (COUT % 4 == 0 && a.out_planar) {
+        if (COUT % 8 == 0 && a.out_split) { store_split<(COUT % 8 == 0 ? COUT : 8)>(a.out, a.out_stride, out_base + i, v, a.range_flag); }
+        else if (COUT % 4 == 0 && a.out_planar) {
             float4* out4 = reinterpret_cast<float4*>(a.out);
 #pragma unroll
             for (int j4 = 0; j4 < COUT / 4; ++j4) {
