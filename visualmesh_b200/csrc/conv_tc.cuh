@@ -18,6 +18,7 @@
 #pragma once
 
 #include <cuda_fp16.h>
+#include <type_traits>
 #include <cuda_runtime.h>
 
 #include "kernels.cuh"
@@ -395,12 +396,7 @@ namespace tc {
                         for (int j = 0; j < NP; ++j) v[j] = __fdiv_rn(v[j], total);
                     }
                     else {
-#pragma unroll
-                        for (int j = 0; j < NP; ++j) {
-                            v[j] = a.activation == VM_SELU ? selu(v[j])
-                                   : a.activation == VM_RELU ? ((v[j] < 0.0f) ? 0.0f : v[j])
-                                                             : tanhf(v[j]);
-                        }
+                        activate<NP>(v, a.activation);  // one branch on the activation, then NP independent chains
                     }
                     if (a.out_split && t.cout == NP) { store_split<NP>(a.out, a.out_stride, out_row, v, a.range_flag); }
                     else if (a.out_planar) {
@@ -439,49 +435,81 @@ namespace tc {
         }
     }
 
-    // ---- the same layer fed from the split feature layout ---------------------------------------------------------
-    // When the producing layer has already stored its output as fp16 hi/lo planes (store_split), assembling the A tile
-    // is a pure copy: each gather thread issues 16-byte cp.async copies from the neighbour's planes straight into the
-    // stage (the planes have the UMMA chunk shape), several slots ahead, with no registers and no arithmetic in between.
-    __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    // ---- the same layer with the A operand in tensor memory -------------------------------------------------------
+    // The split layout holds every feature row as fp16 hi chunks and lo chunks, which is exactly what the MMA wants of
+    // one row of A. Here a gather thread (thread = row) loads its neighbour's chunks with 16-byte loads and writes them
+    // straight into tensor-memory columns of its own lane (tcgen05.st); the MMA takes A from tensor memory and only the
+    // weights from shared memory. The gathered tile never passes through shared memory, so the load/store data pipe
+    // carries the gather once (as in the FFMA kernels) instead of three times (copy in, tensor-core read, conflicts).
+    // The unit of work is one K step: 16 channels of one slot = two hi and two lo chunks = 16 columns of tensor memory.
+    // Loads run DEPTH - 1 units ahead in registers, across tile boundaries; the register buffer of a unit is chosen at
+    // compile time, so the tile body exists once per phase of the (units per tile) mod DEPTH cycle.
+    __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint4& x, const uint4& y) {
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(x.x), "r"(x.y),
+                     "r"(x.z), "r"(x.w), "r"(y.x), "r"(y.y), "r"(y.z), "r"(y.w)
+                     : "memory");
     }
-    __device__ __forceinline__ void cp_async_commit() {
-        asm volatile("cp.async.commit_group;" ::: "memory");
+    // A read-only 16-byte load that stays where it is written: the compiler may sink a plain __ldg down to its first
+    // use, which would undo the software pipelining; volatile asm statements keep their order.
+    __device__ __forceinline__ uint4 load_early(const uint4* p) {
+        uint4 v;
+        asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+        return v;
     }
-    template <int N>
-    __device__ __forceinline__ void cp_async_wait() {
-        asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+    __device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+        asm volatile(
+          "{\n\t"
+          ".reg .pred p;\n\t"
+          "setp.ne.b32 p, %4, 0;\n\t"
+          "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+          "}\n" ::"r"(tmem_d),
+          "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+          : "memory");
     }
 
-    template <int CIN, int NP, int STAGES>
-    constexpr size_t smem_bytes_split(int n_slots) {
-        return 256 + static_cast<size_t>(STAGES) * 2 * (CIN / 8) * TILE_ROWS * 16 + static_cast<size_t>(n_slots) * (CIN / 8) * 2 * NP * 16;
+    constexpr int LOAD_DEPTH = 3;  // register buffers of gathered units per thread
+
+    // two accumulators of 2 NP columns, then the stages of A: 8 columns of hi pairs and 8 of lo pairs per K step
+    template <int NP>
+    __host__ __device__ constexpr int tmem_a_stages() {
+        return NP == 16 ? 4 : 8;
+    }
+    template <int NP>
+    __host__ __device__ constexpr int tmem_columns() {
+        return 4 * NP + tmem_a_stages<NP>() * 16;  // 128 or 256: powers of two as the allocator wants
+    }
+    template <int CIN, int NP>
+    constexpr size_t smem_bytes_tmem(int n_slots) {
+        return 256 + static_cast<size_t>(n_slots) * (CIN / 8) * 2 * NP * 16;
     }
 
-    template <int CIN, int NP, int STAGES, int NSLOTS>
-    __global__ void __launch_bounds__(CTA_THREADS) k_graph_conv_tc_split(const ConvArgs a, const Args t) {
+    template <int CIN, int NP, int NSLOTS>
+    __global__ void __launch_bounds__(CTA_THREADS, NP == 16 ? 3 : 2) k_graph_conv_tc_tmem(const ConvArgs a, const Args t) {
         static_assert(NP == 16 || NP == 32, "unsupported tile width");
         static_assert(CIN % 16 == 0, "a slot must hold whole K steps of 16 fp16 channels");
-        constexpr int PLANES     = CIN / 8;
-        constexpr int PLANE      = TILE_ROWS * 16;
-        constexpr int SLOT_BYTES = PLANES * PLANE;
-        constexpr int WCHUNK     = 2 * NP * 16;
-        constexpr int TMEM_COLS  = 4 * NP;
-        constexpr int AHEAD      = STAGES - 1 < NSLOTS ? STAGES - 1 : NSLOTS;  // slots in flight ahead of the one handed over
+        constexpr int PLANES    = CIN / 8;   // 16-byte chunks of the hi (or lo) half of a row
+        constexpr int KSTEPS    = CIN / 16;  // K steps (units) per slot
+        constexpr int UNITS     = NSLOTS * KSTEPS;
+        constexpr int STAGES    = tmem_a_stages<NP>();
+        constexpr int DEPTH     = LOAD_DEPTH;
+        constexpr int WCHUNK    = 2 * NP * 16;
+        constexpr int D_COLS    = 4 * NP;
+        constexpr int TMEM_COLS = tmem_columns<NP>();
+        static_assert(UNITS >= DEPTH - 1, "the prologue loads DEPTH - 1 units of the first tile");
+        static_assert(DEPTH == 3, "the tile loop below is written out for three phases");
 
         extern __shared__ __align__(1024) unsigned char smem_raw[];
         __shared__ uint64_t bars[2 * STAGES + 4];
         __shared__ uint32_t tmem_base_slot;
         __shared__ int32_t tile_prefix[MAX_FRAMES + 1];
+        __shared__ int32_t frame_start[MAX_FRAMES + 1];  // offsets[f0 + f]: first compact node of frame f
         __shared__ int32_t failed_s;
         volatile int32_t* failed = &failed_s;
 
         const int tid  = threadIdx.x;
         const int warp = tid >> 5;
         const int lane = tid & 31;
-        unsigned char* stage_base = smem_raw;
-        unsigned char* w_s        = smem_raw + static_cast<size_t>(STAGES) * 2 * SLOT_BYTES;
+        unsigned char* w_s           = smem_raw;
         const uint32_t bar_full      = smem_u32(&bars[0]);
         const uint32_t bar_empty     = smem_u32(&bars[STAGES]);
         const uint32_t bar_acc_full  = smem_u32(&bars[2 * STAGES]);
@@ -498,10 +526,14 @@ namespace tc {
                 mbar_init(bar_acc_empty + 8 * i, PRODUCER_WARPS);
             }
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        for (int f = tid; f <= t.n_frames; f += CTA_THREADS) frame_start[f] = a.offsets[a.f0 + f];
+        __syncthreads();
+        if (tid == 0) {
             int run = 0;
             for (int f = 0; f < t.n_frames; ++f) {
                 tile_prefix[f] = run;
-                const int rows = a.offsets[a.f0 + f + 1] - a.offsets[a.f0 + f] + 1;
+                const int rows = frame_start[f + 1] - frame_start[f] + 1;
                 run += (rows + TILE_ROWS - 1) / TILE_ROWS;
             }
             tile_prefix[t.n_frames] = run;
@@ -521,6 +553,7 @@ namespace tc {
         __syncthreads();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_base = tmem_base_slot;
+        const uint32_t a_base    = tmem_base + D_COLS;
         const int total_tiles    = tile_prefix[t.n_frames];
 
         if (warp == PRODUCER_WARPS) {
@@ -530,7 +563,6 @@ namespace tc {
                 constexpr uint32_t IDESC_CAT  = IDESC_BASE | (static_cast<uint32_t>((2 * NP) >> 3) << 17);
                 constexpr uint32_t IDESC_HI   = IDESC_BASE | (static_cast<uint32_t>(NP >> 3) << 17);
                 const uint32_t w_addr = smem_u32(w_s);
-                const uint32_t a_addr = smem_u32(stage_base);
                 uint32_t it = 0, tile_count = 0;
                 bool ok = true;
                 for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
@@ -540,7 +572,7 @@ namespace tc {
                         ok = false;
                         break;
                     }
-                    for (int s = 0; s < NSLOTS; ++s, ++it) {
+                    for (int u = 0; u < UNITS; ++u, ++it) {
                         const uint32_t stage = it % STAGES;
                         const uint32_t use   = it / STAGES;
                         if (!mbar_wait_or_fail(bar_full + 8 * stage, use & 1u, failed)) {
@@ -548,101 +580,119 @@ namespace tc {
                             break;
                         }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint32_t a_hi = a_addr + stage * 2 * SLOT_BYTES;
-                        const uint32_t a_lo = a_hi + SLOT_BYTES;
-#pragma unroll
-                        for (int ks = 0; ks < PLANES / 2; ++ks) {
-                            const uint64_t da_hi = smem_desc(a_hi + ks * 2 * PLANE, PLANE, 128);
-                            const uint64_t da_lo = smem_desc(a_lo + ks * 2 * PLANE, PLANE, 128);
-                            const uint64_t db    = smem_desc(w_addr + (s * PLANES + ks * 2) * WCHUNK, WCHUNK, 128);
-                            mma<true>(acc, da_hi, db, IDESC_CAT, (s == 0 && ks == 0) ? 0u : 1u);
-                            mma<true>(acc, da_lo, db, IDESC_HI, 1u);
-                        }
+                        const uint32_t a_hi = a_base + stage * 16;
+                        const uint64_t db   = smem_desc(w_addr + u * 2 * WCHUNK, WCHUNK, 128);  // chunks 2u and 2u + 1 of K
+                        mma_f16_ts(acc, a_hi, db, IDESC_CAT, u == 0 ? 0u : 1u);
+                        mma_f16_ts(acc, a_hi + 8, db, IDESC_HI, 1u);
                         commit(bar_empty + 8 * stage);
-                        if (s == NSLOTS - 1) commit(bar_acc_full + 8 * ab);
+                        if (u == UNITS - 1) commit(bar_acc_full + 8 * ab);
                     }
                 }
                 if (!ok) failed_s = 1;
             }
         }
         else {
-            // ================= copy issuers + epilogue =================
-            const unsigned char* in_b = reinterpret_cast<const unsigned char*>(a.in);
-            const uint32_t a_addr     = smem_u32(stage_base);
+            // ================= gather + epilogue =================
+            const uint4* in4         = reinterpret_cast<const uint4*>(a.in);
+            const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;  // this warp's quarter of the 128 lanes
             uint32_t tile_count = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
-                int f = 0;
+
+            struct TileRef {
+                int rows;        // rows of the tile's frame, sentinel row included
+                int row;         // this thread's row within the frame
+                int local_base;  // first feature row of the frame in this launch
+                size_t nb_base;  // first neighbourhood / global output row of the frame
+            };
+            int frame_hint = 0;  // tiles only move forward: the search resumes at the frame of the last tile located
+            auto locate = [&](int tile) {
+                int f = frame_hint;
                 while (f + 1 < t.n_frames && tile_prefix[f + 1] <= tile) ++f;
-                const int frame      = a.f0 + f;
-                const int start      = a.offsets[frame];
-                const int rows       = a.offsets[frame + 1] - start + 1;
-                const int row        = (tile - tile_prefix[f]) * TILE_ROWS + tid;
-                const int rowc       = min(row, rows - 1);
-                const int local_base = start - a.offsets[a.f0] + f;
-                const size_t nb_base = static_cast<size_t>(start + frame);
-                const uint32_t ab    = tile_count & 1u;
-                const uint32_t acc   = tmem_base + ab * (2 * NP);
-                const uint32_t it0   = tile_count * NSLOTS;
-
-                int src_rows[NSLOTS];
-                src_rows[0] = local_base + rowc;
+                frame_hint      = f;
+                const int start = frame_start[f];
+                TileRef r;
+                r.rows       = frame_start[f + 1] - start + 1;
+                r.row        = (tile - tile_prefix[f]) * TILE_ROWS + tid;
+                r.local_base = start - frame_start[0] + f;
+                r.nb_base    = static_cast<size_t>(start + a.f0 + f);
+                return r;
+            };
+            // Source rows relative to the frame's first feature row. The neighbour indices come from HBM and nothing
+            // may touch them before they are needed (an add right behind the load would stall the thread for the whole
+            // memory latency): the frame's base is added where the row is used.
+            auto fetch_rows = [&](const TileRef& r, int (&src)[NSLOTS]) {
+                const int rowc = min(r.row, r.rows - 1);
+                src[0]         = rowc;
 #pragma unroll
-                for (int s = 1; s < NSLOTS; ++s) src_rows[s] = local_base + __ldg(a.nb + (nb_base + rowc) * a.n_neighbours + (s - 1));
+                for (int s = 1; s < NSLOTS; ++s) src[s] = __ldg(a.nb + (r.nb_base + rowc) * a.n_neighbours + (s - 1));
+            };
+            auto arrived_value = [](int x) {
+                asm volatile("" : "+r"(x));  // pins the first use of a loaded value to this point of the program
+                return x;
+            };
+            uint4 buf[DEPTH][4];  // two hi chunks and two lo chunks of up to DEPTH gathered units
+            auto load = [&](uint4 (&b)[4], int src_row, int ks) {
+                b[0] = load_early(in4 + static_cast<size_t>(2 * ks) * a.in_stride + src_row);
+                b[1] = load_early(in4 + static_cast<size_t>(2 * ks + 1) * a.in_stride + src_row);
+                b[2] = load_early(in4 + static_cast<size_t>(PLANES + 2 * ks) * a.in_stride + src_row);
+                b[3] = load_early(in4 + static_cast<size_t>(PLANES + 2 * ks + 1) * a.in_stride + src_row);
+            };
 
-                // issue the copies of slot s into its stage (after the MMAs of the stage's previous use have read it)
-                auto issue = [&](int s) {
-                    const uint32_t it    = it0 + s;
+            int cur[NSLOTS], nxt[NSLOTS];
+            TileRef cr = {1, 0, 0, 0}, nr = {1, 0, 0, 0};
+            int tile = blockIdx.x;
+            if (tile < total_tiles) {
+                cr = locate(tile);
+                fetch_rows(cr, cur);
+#pragma unroll
+                for (int u = 0; u < DEPTH - 1; ++u) load(buf[u], cr.local_base + arrived_value(cur[u / KSTEPS]), u % KSTEPS);
+            }
+
+            // one tile; PH = (units handled before this tile) mod DEPTH selects the register buffers at compile time
+            auto do_tile = [&](auto phase) -> bool {
+                constexpr int PH = decltype(phase)::value;
+                if (tile >= total_tiles || !ok) return false;
+                const uint32_t ab   = tile_count & 1u;
+                const uint32_t acc  = tmem_base + ab * (2 * NP);
+                const uint32_t it0  = tile_count * UNITS;
+                const bool has_next = tile + static_cast<int>(gridDim.x) < total_tiles;
+                if (has_next) {
+                    nr = locate(tile + gridDim.x);
+                    fetch_rows(nr, nxt);
+                }
+#pragma unroll
+                for (int u = 0; u < UNITS; ++u) {
+                    constexpr int AHEAD = DEPTH - 1;
+                    const int ua        = u + AHEAD;  // the unit whose loads start now
+                    if (ua < UNITS) { load(buf[(PH + ua) % DEPTH], cr.local_base + arrived_value(cur[ua / KSTEPS]), ua % KSTEPS); }
+                    else if (has_next) {
+                        load(buf[(PH + ua) % DEPTH], nr.local_base + arrived_value(nxt[(ua - UNITS) / KSTEPS]), (ua - UNITS) % KSTEPS);
+                    }
+                    const uint32_t it    = it0 + u;
                     const uint32_t stage = it % STAGES;
                     const uint32_t use   = it / STAGES;
                     if (use > 0 && !mbar_wait_or_fail(bar_empty + 8 * stage, (use - 1) & 1u, failed)) ok = false;
-                    const uint32_t hi = a_addr + stage * 2 * SLOT_BYTES + tid * 16;
-                    const uint32_t lo = hi + SLOT_BYTES;
-#pragma unroll
-                    for (int p = 0; p < PLANES; ++p) {
-                        cp_async16(hi + p * PLANE, in_b + (static_cast<size_t>(p) * a.in_stride + src_rows[s]) * 16);
-                        cp_async16(lo + p * PLANE, in_b + (static_cast<size_t>(PLANES + p) * a.in_stride + src_rows[s]) * 16);
-                    }
-                    cp_async_commit();
-                };
-#pragma unroll
-                for (int s = 0; s < AHEAD; ++s) issue(s);
-#pragma unroll
-                for (int s = 0; s < NSLOTS; ++s) {
-                    if (s + AHEAD < NSLOTS) {
-                        issue(s + AHEAD);
-                        cp_async_wait<AHEAD>();  // everything but the AHEAD newest groups has landed: slot s is in
-                    }
-                    else {
-                        // no newer group was issued: groups still allowed in flight = slots after s
-                        switch (NSLOTS - 1 - s) {
-                            case 0: cp_async_wait<0>(); break;
-                            case 1: cp_async_wait<1>(); break;
-                            case 2: cp_async_wait<2>(); break;
-                            case 3: cp_async_wait<3>(); break;
-                            case 4: cp_async_wait<4>(); break;
-                            case 5: cp_async_wait<5>(); break;
-                            case 6: cp_async_wait<6>(); break;
-                            default: cp_async_wait<7>(); break;
-                        }
-                    }
-                    // this thread's copies of slot s are in shared memory: publish them to the tensor core
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint4(&b)[4]  = buf[(PH + u) % DEPTH];
+                    const uint32_t a_hi = a_base + lane_base + stage * 16;
+                    tmem_st8(a_hi, b[0], b[1]);
+                    tmem_st8(a_hi + 8, b[2], b[3]);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_full + 8 * ((it0 + s) % STAGES));
+                    if (lane == 0) mbar_arrive(bar_full + 8 * stage);
                 }
                 ok = __all_sync(0xffffffffu, ok) && !*failed;
-                if (!ok) break;
-
+                if (!ok) return false;
                 const bool arrived = mbar_wait_or_fail(bar_acc_full + 8 * ab, (tile_count >> 1) & 1u, failed);
                 ok                 = __all_sync(0xffffffffu, arrived);
-                if (!ok) break;
+                if (!ok) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 float v[NP];
 #pragma unroll
                 for (int j0 = 0; j0 < 2 * NP; j0 += 16) {
                     uint32_t r[16];
-                    const uint32_t taddr = acc + (static_cast<uint32_t>(warp * 32) << 16) + j0;
+                    const uint32_t taddr = acc + lane_base + j0;
                     asm volatile(
                       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
                       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
@@ -662,8 +712,8 @@ namespace tc {
                 if (lane == 0) mbar_arrive(bar_acc_empty + 8 * ab);
 #pragma unroll
                 for (int j = 0; j < NP; ++j) v[j] = v[j] + __ldg(t.bias + j);
-                if (row < rows) {
-                    const size_t out_row = (a.out_global ? nb_base : static_cast<size_t>(local_base)) + row;
+                if (cr.row < cr.rows) {
+                    const size_t out_row = (a.out_global ? cr.nb_base : static_cast<size_t>(cr.local_base)) + cr.row;
                     if (a.activation == VM_SOFTMAX) {
                         float total = 0.0f;
 #pragma unroll
@@ -677,12 +727,7 @@ namespace tc {
                         for (int j = 0; j < NP; ++j) v[j] = __fdiv_rn(v[j], total);
                     }
                     else {
-#pragma unroll
-                        for (int j = 0; j < NP; ++j) {
-                            v[j] = a.activation == VM_SELU ? selu(v[j])
-                                   : a.activation == VM_RELU ? ((v[j] < 0.0f) ? 0.0f : v[j])
-                                                             : tanhf(v[j]);
-                        }
+                        activate<NP>(v, a.activation);  // one branch on the activation, then NP independent chains
                     }
                     if (a.out_split && t.cout == NP) { store_split<NP>(a.out, a.out_stride, out_row, v, a.range_flag); }
                     else if (a.out_planar) {
@@ -702,9 +747,17 @@ namespace tc {
                         }
                     }
                 }
-            }
+                cr = nr;
+#pragma unroll
+                for (int s = 0; s < NSLOTS; ++s) cur[s] = nxt[s];
+                tile += gridDim.x;
+                ++tile_count;
+                return true;
+            };
+            // DEPTH tiles bring the phase back to where it started
+            while (do_tile(std::integral_constant<int, 0>{}) && do_tile(std::integral_constant<int, UNITS % DEPTH>{})
+                   && do_tile(std::integral_constant<int, (2 * UNITS) % DEPTH>{})) {}
             if (!ok && lane == 0) failed_s = 1;
-            cp_async_wait<0>();
         }
 
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

@@ -314,24 +314,26 @@ static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frame
 }
 
 template <int CIN, int NP, int NSLOTS>
-static void launch_conv_tc_split_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
-    constexpr int STAGES = CIN >= 32 ? 3 : 4;
-    const size_t smem    = tc::smem_bytes_split<CIN, NP, STAGES>(NSLOTS);
+static void launch_conv_tc_tmem_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
+    const size_t smem = tc::smem_bytes_tmem<CIN, NP>(NSLOTS);
     static int ctas_per_sm = 0;
     static int n_sms       = 0;
     if (ctas_per_sm == 0) {
-        VM_CUDA(cudaFuncSetAttribute(tc::k_graph_conv_tc_split<CIN, NP, STAGES, NSLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (smem > 48 * 1024) {
+            VM_CUDA(cudaFuncSetAttribute(tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        }
         int dev = 0;
         VM_CUDA(cudaGetDevice(&dev));
         VM_CUDA(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
         const int by_smem = static_cast<int>((220 * 1024) / (smem + 2048));
-        const int by_tmem = 512 / (4 * NP);
+        const int by_tmem = 512 / tc::tmem_columns<NP>();
         cudaFuncAttributes attr;
-        VM_CUDA(cudaFuncGetAttributes(&attr, tc::k_graph_conv_tc_split<CIN, NP, STAGES, NSLOTS>));
-        const int regs_per_cta = ((attr.numRegs + 7) / 8 * 8) * tc::CTA_THREADS;
-        const int by_regs      = 65536 / std::max(1, regs_per_cta);
-        ctas_per_sm            = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
-        if (const char* v = std::getenv("VMCUDA_TC_CTAS")) ctas_per_sm = std::max(1, std::atoi(v));
+        VM_CUDA(cudaFuncGetAttributes(&attr, tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS>));
+        // registers: 8 per thread at a time, 512 per warp at a time, 64 K per SM
+        const int regs_per_warp = (((attr.numRegs + 7) / 8 * 8) * 32 + 511) / 512 * 512;
+        const int by_regs       = 65536 / std::max(1, regs_per_warp * (tc::CTA_THREADS / 32));
+        ctas_per_sm             = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
+        if (const char* v = std::getenv("VMCUDA_TC_CTAS")) ctas_per_sm = std::max(1, std::min(ctas_per_sm, std::atoi(v)));
     }
     tc::Args t{};
     t.w_cat      = L.d_tc_cat;
@@ -341,7 +343,7 @@ static void launch_conv_tc_split_t(const DenseLayer& L, const ConvArgs& a, int n
     t.abort_flag = abort_flag;
     const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
     const int grid        = std::max(1, std::min(tiles_upper, n_sms * ctas_per_sm));
-    tc::k_graph_conv_tc_split<CIN, NP, STAGES, NSLOTS><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
+    tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
 }
 
 // The tensor-core kernel fed from the split feature layout exists for these shapes.
@@ -352,7 +354,7 @@ static bool has_tc_split_kernel(const DenseLayer& L) {
 static bool launch_conv_tc_split(vm_engine* e, const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, cudaStream_t s) {
 #define VM_TCS(CI, NPAD, NS)                                                              \
     if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS) {                               \
-        launch_conv_tc_split_t<CI, NPAD, NS>(L, a, n_frames, max_rows, e->d_abort, s);     \
+        launch_conv_tc_tmem_t<CI, NPAD, NS>(L, a, n_frames, max_rows, e->d_abort, s);       \
         return true;                                                                       \
     }
     VM_TCS(16, 16, 5) VM_TCS(16, 16, 7) VM_TCS(16, 16, 9) VM_TCS(16, 32, 5) VM_TCS(16, 32, 7) VM_TCS(16, 32, 9)

@@ -290,7 +290,10 @@ __global__ void __launch_bounds__(ROW_THREADS) k_sample_flat(const float2* __res
 __device__ __forceinline__ float selu(float s) {
     const float lambda = 1.0507009873554804934193349852946f;
     const float alpha  = 1.6732632423543772848170429916717f;
-    return __fmul_rn(lambda, (s >= 0.0f) ? s : __fsub_rn(__fmul_rn(alpha, expf(s)), alpha));
+    // exp is evaluated on min(s, 0) for every value and the result selected: straight-line code, so the chains of a
+    // row's outputs overlap instead of running one branch after the other; the value is the same bit for bit
+    const float negative = __fsub_rn(__fmul_rn(alpha, expf(fminf(s, 0.0f))), alpha);
+    return __fmul_rn(lambda, (s >= 0.0f) ? s : negative);
 }
 
 template <int COUT>
