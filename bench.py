@@ -37,7 +37,12 @@ from visualmesh_b200 import workloads as W  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture summarised in
 # profiles/ (None until captured); scaled to the launch's rows when the capture ran a smaller case.
-NCU_TRAFFIC_BYTES_PER_ROW = 119.2  # profiles/graph_conv_16x16_cfg1_16frames.md: 132.1 MB over 1,108,261 rows
+# DRAM traffic per row of the dominant kernels from their ncu captures (dram__bytes_read + dram__bytes_write over the
+# rows of the captured launch); traffic grows in proportion to the rows, so it is scaled to the bench's launches.
+NCU_TRAFFIC_BYTES_PER_ROW = {
+    (16, 16): 119.6,  # profiles/graph_conv_16x16_cfg1_16frames.md: 132.6 MB over 1,108,261 rows
+    (32, 32): 250.4,  # profiles/graph_conv_tc_tmem_32x32_cfg3_1frame.md: 233.3 MB over 931,718 rows
+}
 
 
 def _peaks():
@@ -331,8 +336,8 @@ def run_ours(args, rank, world, local_rank):
     achieved = bytes_per_row * rows_total / top_s / 1e9
     roofline = {"bound": "hbm", "kernel": f"k_graph_conv<{cin},{cout}>", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                "traffic": (NCU_TRAFFIC_BYTES_PER_ROW * rows_total / stage_launches[top])
-                if NCU_TRAFFIC_BYTES_PER_ROW else None,
+                "traffic": (NCU_TRAFFIC_BYTES_PER_ROW[(cin, cout)] * rows_total / stage_launches[top])
+                if (cin, cout) in NCU_TRAFFIC_BYTES_PER_ROW else None,
                 "algorithmic_bytes_per_launch": bytes_per_row * rows_total / stage_launches[top],
                 "avg_launch_ms": stage_total[top] / stage_launches[top],
                 "fp32_tflops": 2.0 * (N + 1) * cin * cout * rows_total / top_s / 1e12,

@@ -496,7 +496,7 @@ namespace tc {
         constexpr int D_COLS    = 4 * NP;
         constexpr int TMEM_COLS = tmem_columns<NP>();
         static_assert(UNITS >= DEPTH - 1, "the prologue loads DEPTH - 1 units of the first tile");
-        static_assert(DEPTH == 3, "the tile loop below is written out for three phases");
+        static_assert(DEPTH == 2 || DEPTH == 3, "the tile loop below is written out for two or three phases");
 
         extern __shared__ __align__(1024) unsigned char smem_raw[];
         __shared__ uint64_t bars[2 * STAGES + 4];
@@ -756,7 +756,7 @@ namespace tc {
             };
             // DEPTH tiles bring the phase back to where it started
             while (do_tile(std::integral_constant<int, 0>{}) && do_tile(std::integral_constant<int, UNITS % DEPTH>{})
-                   && do_tile(std::integral_constant<int, (2 * UNITS) % DEPTH>{})) {}
+                   && (DEPTH == 2 || do_tile(std::integral_constant<int, (2 * UNITS) % DEPTH>{}))) {}
             if (!ok && lane == 0) failed_s = 1;
         }
 
