@@ -278,6 +278,22 @@ def test_tensor_core_layers_match_the_oracle(n_neighbours, widths):
         engine.close()
 
 
+@pytest.mark.parametrize("n_neighbours,widths", [(6, [16, 16, 16, 3]), (8, [32, 32, 4])])
+def test_tensor_core_layers_over_many_tiles_per_cta(n_neighbours, widths):
+    """More 128-row tiles than resident CTAs: every CTA walks several tiles, so the loads that run ahead across tile
+    boundaries, the double-buffered accumulators and every phase of the register-buffer rotation are exercised."""
+    net = W.make_network(21, n_neighbours, widths)
+    x, nb = _random_rows(150_001, n_neighbours, 23)
+    want = O.network(x, nb, net)
+    engine = _engine_with_tc(net, 2)
+    for _ in range(2):
+        got = engine.network(x, nb)
+        d = np.abs(got.astype(np.float64) - want.astype(np.float64)).max()
+        print(f"N={n_neighbours} widths={widths}, 1172 tiles: max |d| = {d:.3g}")
+        assert d <= P.TOL_CLS / 4
+    engine.close()
+
+
 def test_tensor_core_range_fallback():
     """Features beyond the range of the fp16 split make the engine recompute with the FFMA kernels, transparently:
     the result is bit for bit what an engine without tensor-core kernels returns."""
