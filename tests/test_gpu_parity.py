@@ -240,6 +240,24 @@ def test_config3_dense_mesh_projection_and_two_layers():
     engine.close()
 
 
+@needs_ref
+def test_config3_dense_mesh_through_the_tensor_core_layers():
+    """Config 3's frame (0.93M rows = 7280 tiles) through first layer, two 32 -> 32 layers on the tensor cores (default
+    policy) and the softmax layer, against the reference CPU engine on the same mesh: the whole call at full size."""
+    wl = W.config(3, n_frames=1)
+    fr = wl.frames[0]
+    net = wl.network[:3] + [[W.Layer(wl.network[-1][0].weights, wl.network[-1][0].biases, W.SOFTMAX)]]
+    ref_mesh = R.RefMesh(fr.mesh)
+    image = fr.image()
+    ref = ref_mesh.classify(net, fr.Hoc, fr.lens, image, fr.format)
+    engine = Engine(net)
+    out = engine.run_batch([FrameInput(Mesh.from_spec(fr.mesh), fr.Hoc, fr.lens, image, fr.format, None)]).frame(0)
+    rep = P.compare(out, ref, fr.lens.dimensions)
+    print(f"cfg3 (4 layers, tcgen05): {rep}")
+    assert rep.ok and rep.n_ref > 900000, str(rep)
+    engine.close()
+
+
 # ---- tensor-core graph convolution (tcgen05) ---------------------------------------------------------------------------
 
 def _engine_with_tc(network, mode):
