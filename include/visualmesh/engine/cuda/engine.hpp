@@ -153,8 +153,16 @@ namespace engine {
 
             /// Drops the device copies of all meshes seen so far
             void clear_cache() {
-                for (auto& m : meshes) vm_mesh_release(engine, m.second);
+                for (auto& m : meshes) vm_mesh_release(engine, m.second.handle);
                 meshes.clear();
+            }
+
+            /// Bounds the number of meshes kept on the device (0 = unbounded, the default, like the OpenCL engine's
+            /// grow-only cache): beyond it the least recently used mesh is released. For a VisualMesh with many
+            /// heights in a long-running process (the role of tensorflow/mesh_cache.hpp:119-159 in training).
+            void set_cache_limit(std::size_t n_meshes) {
+                cache_limit = n_meshes;
+                evict();
             }
 
             template <template <typename> class Model>
@@ -216,7 +224,10 @@ namespace engine {
             template <template <typename> class Model>
             vm_mesh* device_mesh(const Mesh<Scalar, Model>& mesh) const {
                 auto it = meshes.find(&mesh);
-                if (it != meshes.end()) return it->second;
+                if (it != meshes.end()) {
+                    it->second.last_use = ++use_counter;
+                    return it->second.handle;
+                }
                 static constexpr int N = Model<Scalar>::N_NEIGHBOURS;
                 const std::size_t n    = mesh.nodes.size();
                 std::vector<float> rays(3 * n);
@@ -233,8 +244,20 @@ namespace engine {
                     Mesh<float, detail::BspAccess>::flatten(mesh, ranges, children, cones);
                     check(vm_mesh_set_bsp(engine, handle, int32_t(ranges.size() / 2), ranges.data(), children.data(), cones.data()));
                 }
-                meshes[&mesh] = handle;
+                meshes[&mesh] = CachedMesh{handle, ++use_counter};
+                evict();
                 return handle;
+            }
+
+            void evict() const {
+                while (cache_limit != 0 && meshes.size() > cache_limit) {
+                    auto oldest = meshes.begin();
+                    for (auto it = meshes.begin(); it != meshes.end(); ++it) {
+                        if (it->second.last_use < oldest->second.last_use) oldest = it;
+                    }
+                    vm_mesh_release(engine, oldest->second.handle);
+                    meshes.erase(oldest);
+                }
             }
 
             template <template <typename> class Model>
@@ -299,7 +322,13 @@ namespace engine {
             bool has_network  = false;
             bool device_lookup;
             /// Device meshes by the address of the Mesh they were uploaded from
-            mutable std::map<const void*, vm_mesh*> meshes;
+            struct CachedMesh {
+                vm_mesh* handle;
+                std::uint64_t last_use;
+            };
+            mutable std::map<const void*, CachedMesh> meshes;
+            mutable std::uint64_t use_counter = 0;
+            std::size_t cache_limit           = 0;
         };
 
     }  // namespace cuda

@@ -346,6 +346,28 @@ def test_network_shaped_like_the_reference_example_model(cases):
     engine.close()
 
 
+def test_mesh_cache_bound_releases_the_least_recently_used_mesh():
+    """cfg4's four heights through an engine that may keep two meshes on the device: results are those of an unbounded
+    engine, and the cache never holds more than two."""
+    wl = W.config(4, n_frames=8)
+    meshes = {}
+    frames = []
+    for fr in wl.frames:
+        mesh = meshes.setdefault(id(fr.mesh), Mesh.from_spec(fr.mesh))
+        frames.append(FrameInput(mesh, fr.Hoc, fr.lens, fr.image(), fr.format, None))
+    assert len(meshes) >= 3
+    plain, bounded = Engine(wl.network), Engine(wl.network, max_cached_meshes=2)
+    for fr in frames:  # one frame per call, heights alternating: every eviction path is taken
+        want = plain(fr.mesh, fr.Hoc, fr.lens, fr.image, fr.format)
+        got = bounded(fr.mesh, fr.Hoc, fr.lens, fr.image, fr.format)
+        assert len(bounded._meshes) <= 2
+        assert np.array_equal(got.global_indices, want.global_indices)
+        assert np.array_equal(G.bits(got.classifications), G.bits(want.classifications))
+    assert len(plain._meshes) == len(meshes)
+    plain.close()
+    bounded.close()
+
+
 def test_visualmesh_height_table_through_the_engine():
     """The VisualMesh overloads (cpp/visualmesh/engine/cpu/engine.hpp:160-165, :289-296): the engine picks the table
     nearest to Hoc[2][3] and gives what a call on that Mesh gives."""

@@ -217,8 +217,12 @@ class BatchResult:
 class Engine:
     """visualmesh::engine::cuda::Engine<float>: the reference engine interface backed by the sm_100a kernels."""
 
-    def __init__(self, structure=None, device: int = -1):
+    def __init__(self, structure=None, device: int = -1, max_cached_meshes: Optional[int] = None):
+        """max_cached_meshes: keep at most this many meshes on the device, releasing the least recently used one
+        (None = unbounded, like the OpenCL engine's grow-only cache). A prepared batch refers to device meshes by
+        handle: with a bound, prepare it again after other meshes have gone through the engine."""
         self._lib = abi.load()
+        self._max_cached_meshes = max_cached_meshes
         self._ptr = None
         structure = structure or []
         flat = [layer for group in structure for layer in group]
@@ -261,6 +265,7 @@ class Engine:
     def _device_mesh(self, mesh: Mesh):
         hit = self._meshes.get(id(mesh))
         if hit is not None:
+            self._meshes[id(mesh)] = self._meshes.pop(id(mesh))  # most recently used goes last
             return hit[1]
         handle = C.c_void_p()
         abi.check(self._lib.vm_mesh_upload(self._ptr, mesh.rays.ctypes.data, mesh.neighbours.ctypes.data,
@@ -270,6 +275,9 @@ class Engine:
                                                 mesh.bsp_ranges.ctypes.data, mesh.bsp_children.ctypes.data,
                                                 mesh.bsp_cones.ctypes.data))
         self._meshes[id(mesh)] = (mesh, handle)
+        while self._max_cached_meshes and len(self._meshes) > self._max_cached_meshes:
+            oldest = next(iter(self._meshes))
+            self._lib.vm_mesh_release(self._ptr, self._meshes.pop(oldest)[1])
         return handle
 
     def prepare_batch(self, frames: Sequence[FrameInput]):
