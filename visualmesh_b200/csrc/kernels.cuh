@@ -529,7 +529,7 @@ __device__ __forceinline__ void ffma2(unsigned long long& acc, unsigned long lon
 
 // Accumulators live as pairs of adjacent output columns, each weight pair is one 64-bit constant load shared by the R
 // rows, each input value is duplicated into a pair once per row and k.
-template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS>
+template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS, int NS = 0>
 __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __grid_constant__ ConvWeights<WMAX> wp) {
     static_assert(CIN % 4 == 0, "vector loads of the input rows");
     constexpr int COUTP = (COUT + 3) & ~3;
@@ -539,7 +539,8 @@ __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __g
     const int rows           = a.offsets[frame + 1] - start + 1;
     const int first          = blockIdx.x * (T * R);
     if (first >= rows) return;
-    const int K           = a.n_slots * CIN;
+    const int n_slots     = NS ? NS : a.n_slots;  // NS != 0: the slot loop is unrolled and its loads scheduled across slots
+    const int K           = n_slots * CIN;
     const int local_base  = start - a.offsets[a.f0] + frame_in_chunk;
     const size_t nb_base  = static_cast<size_t>(start + frame);
 
@@ -552,7 +553,8 @@ __global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __g
         for (int j = 0; j < COUTP / 2; ++j) acc[q][j] = pack2(wp.w[K * COUTP + 2 * j], wp.w[K * COUTP + 2 * j + 1]);
     }
     const float4* in4 = reinterpret_cast<const float4*>(a.in);
-    for (int s = 0; s < a.n_slots; ++s) {
+#pragma unroll(NS ? NS : 1)
+    for (int s = 0; s < n_slots; ++s) {
         int src_row[R];
 #pragma unroll
         for (int q = 0; q < R; ++q) {
