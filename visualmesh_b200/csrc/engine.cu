@@ -254,10 +254,12 @@ static bool launch_conv_cw(const DenseLayer& L, const ConvArgs& a, dim3 grid_row
     ConvWeights<WMAX> wp;
     std::memcpy(wp.w, L.host_packed.data(), L.host_packed.size() * sizeof(float));
     dim3 grid((max_rows + T * R - 1) / (T * R), grid_rows.y);
-    // the 8 -> 8 layer is bound by the latency of its gather: with the slot loop unrolled (slot count as a template
-    // parameter) the loads of the next slots are issued ahead of the current slot's arithmetic (measured 15 % faster;
-    // the 16-channel layers, bound by the FP32 pipe, measured 3-6 % slower that way and keep the rolled loop)
-    constexpr bool LATENCY_BOUND = CIN == 8 && COUT == 8;
+    // Layers bound by the latency of their gather rather than by the FP32 pipe - 4-channel first layers, 8 -> 8, and
+    // the narrow last layers - run with the slot loop unrolled (slot count as a template parameter): the loads of the
+    // next slots are then issued ahead of the current slot's arithmetic. Measured on 4.4 M rows: 4 -> 16 183 -> 114 us
+    // (with the weights in the parameter space instead of shared memory), 8 -> 8 133 -> 112 us, 32 -> 4 448 -> 413 us;
+    // the 16- and 32-channel layers in between, bound by the FP32 pipe, measured 3-6 % slower unrolled and stay rolled.
+    constexpr bool LATENCY_BOUND = (CIN == 8 && COUT == 8) || CIN == 4 || COUT <= 4;
     if (LATENCY_BOUND && a.n_slots == 5) { k_graph_conv_cw<CIN, COUT, R, WMAX, T, LATENCY_BOUND ? 5 : 0><<<grid, T, 0, s>>>(a, wp); }
     else if (LATENCY_BOUND && a.n_slots == 7) {
         k_graph_conv_cw<CIN, COUT, R, WMAX, T, LATENCY_BOUND ? 7 : 0><<<grid, T, 0, s>>>(a, wp);
@@ -285,8 +287,8 @@ static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, 
     if (const_weights && L.cin == 16 && L.cout == 16 && launch_conv_cw<16, 16, 2, CW_MAX, 256>(L, a, grid, max_rows, s)) return true;
 #define VM_CONV(CI, CO, RR)                                                                       \
     if (L.cin == CI && L.cout == CO) {                                                            \
-        /* 4-channel first layers are gather-bound and measured faster with the weights in shared memory */ \
-        if (const_weights && CI > 4 && launch_conv_cw<CI, CO, RR, CW_MAX>(L, a, grid, max_rows, s)) return true; \
+        /* parameter-space weights: two rows per thread and 256 threads measured best for every shape tried */ \
+        if (const_weights && launch_conv_cw<CI, CO, 2, CW_MAX, 256>(L, a, grid, max_rows, s)) return true; \
         launch_conv_t<CI, CO, RR>(a, grid, max_rows, s);                                          \
         return true;                                                                              \
     }
