@@ -233,15 +233,35 @@ static bool has_fast_ffma_kernel(int cin, int cout) {
     return false;
 }
 
+// What a launcher works out once per kernel instantiation and device: function attributes are per device, and engine
+// instances of several host threads may reach a launcher at the same time.
+struct LaunchPlan {
+    int ctas_per_sm = 0;
+    int n_sms       = 0;
+};
+constexpr int MAX_DEVICES = 64;
+struct LaunchPlans {
+    LaunchPlan plan[MAX_DEVICES];
+    std::once_flag once[MAX_DEVICES];
+    template <typename Init>
+    const LaunchPlan& get(Init init) {
+        int dev = 0;
+        VM_CUDA(cudaGetDevice(&dev));
+        dev = std::min(std::max(dev, 0), MAX_DEVICES - 1);
+        std::call_once(once[dev], [&] { plan[dev] = init(dev); });
+        return plan[dev];
+    }
+};
+
 template <int CIN, int COUT, int R, int T = CONV_THREADS, int MINB = 1>
 static void launch_conv_t(const ConvArgs& a, dim3 grid_rows, int max_rows, cudaStream_t s) {
     constexpr int COUTP = (COUT + 3) & ~3;
     const size_t smem   = (static_cast<size_t>(a.n_slots) * CIN * COUTP + COUTP) * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
+    static LaunchPlans plans;
+    plans.get([](int) {
         VM_CUDA(cudaFuncSetAttribute(k_graph_conv<CIN, COUT, R, T, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-        configured = true;
-    }
+        return LaunchPlan{};
+    });
     dim3 grid((max_rows + T * R - 1) / (T * R), grid_rows.y);
     k_graph_conv<CIN, COUT, R, T, MINB><<<grid, T, smem, s>>>(a);
 }
@@ -301,22 +321,21 @@ template <int CIN, int NP, int NSLOTS, bool HALF>
 static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
     constexpr int STAGES = CIN >= 32 ? 2 : 3;  // 32-channel stages are 16 KB: two of them leave room for a third CTA per SM
     const size_t smem    = tc::smem_bytes<CIN, NP, STAGES, HALF>(NSLOTS);
-    static int ctas_per_sm = 0;
-    static int n_sms       = 0;
-    if (ctas_per_sm == 0) {
+    static LaunchPlans plans;
+    const LaunchPlan& plan = plans.get([smem](int dev) {
+        LaunchPlan p;
         VM_CUDA(cudaFuncSetAttribute(tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        int dev = 0;
-        VM_CUDA(cudaGetDevice(&dev));
-        VM_CUDA(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
+        VM_CUDA(cudaDeviceGetAttribute(&p.n_sms, cudaDevAttrMultiProcessorCount, dev));
         // resident CTAs per SM: shared memory (about 220 KB usable, some per CTA reserved) and tensor memory (512 columns)
         const int by_smem = static_cast<int>((220 * 1024) / (smem + 2048));
         const int by_tmem = 512 / (4 * NP);
         cudaFuncAttributes attr;
         VM_CUDA(cudaFuncGetAttributes(&attr, tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF>));
-        const int regs_per_cta = ((attr.numRegs + 7) / 8 * 8) * tc::CTA_THREADS;
-        const int by_regs      = 65536 / std::max(1, regs_per_cta);
-        ctas_per_sm            = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
-    }
+        const int regs_per_warp = (((attr.numRegs + 7) / 8 * 8) * 32 + 511) / 512 * 512;
+        const int by_regs       = 65536 / std::max(1, regs_per_warp * (tc::CTA_THREADS / 32));
+        p.ctas_per_sm           = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
+        return p;
+    });
     tc::Args t{};
     t.w_cat      = L.d_tc_cat;
     t.bias       = L.d_tc_bias;
@@ -324,22 +343,20 @@ static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frame
     t.cout       = L.cout;
     t.abort_flag = abort_flag;
     const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
-    const int grid        = std::max(1, std::min(tiles_upper, n_sms * ctas_per_sm));
+    const int grid        = std::max(1, std::min(tiles_upper, plan.n_sms * plan.ctas_per_sm));
     tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
 }
 
 template <int CIN, int NP, int NSLOTS>
 static void launch_conv_tc_tmem_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
     const size_t smem = tc::smem_bytes_tmem<CIN, NP>(NSLOTS);
-    static int ctas_per_sm = 0;
-    static int n_sms       = 0;
-    if (ctas_per_sm == 0) {
+    static LaunchPlans plans;
+    const LaunchPlan& plan = plans.get([smem](int dev) {
+        LaunchPlan p;
         if (smem > 48 * 1024) {
             VM_CUDA(cudaFuncSetAttribute(tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         }
-        int dev = 0;
-        VM_CUDA(cudaGetDevice(&dev));
-        VM_CUDA(cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev));
+        VM_CUDA(cudaDeviceGetAttribute(&p.n_sms, cudaDevAttrMultiProcessorCount, dev));
         const int by_smem = static_cast<int>((220 * 1024) / (smem + 2048));
         const int by_tmem = 512 / tc::tmem_columns<NP>();
         cudaFuncAttributes attr;
@@ -347,9 +364,10 @@ static void launch_conv_tc_tmem_t(const DenseLayer& L, const ConvArgs& a, int n_
         // registers: 8 per thread at a time, 512 per warp at a time, 64 K per SM
         const int regs_per_warp = (((attr.numRegs + 7) / 8 * 8) * 32 + 511) / 512 * 512;
         const int by_regs       = 65536 / std::max(1, regs_per_warp * (tc::CTA_THREADS / 32));
-        ctas_per_sm             = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
-        if (const char* v = std::getenv("VMCUDA_TC_CTAS")) ctas_per_sm = std::max(1, std::min(ctas_per_sm, std::atoi(v)));
-    }
+        p.ctas_per_sm           = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
+        if (const char* v = std::getenv("VMCUDA_TC_CTAS")) p.ctas_per_sm = std::max(1, std::min(p.ctas_per_sm, std::atoi(v)));
+        return p;
+    });
     tc::Args t{};
     t.w_cat      = L.d_tc_cat;
     t.bias       = L.d_tc_bias;
@@ -357,7 +375,7 @@ static void launch_conv_tc_tmem_t(const DenseLayer& L, const ConvArgs& a, int n_
     t.cout       = L.cout;
     t.abort_flag = abort_flag;
     const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
-    const int grid        = std::max(1, std::min(tiles_upper, n_sms * ctas_per_sm));
+    const int grid        = std::max(1, std::min(tiles_upper, plan.n_sms * plan.ctas_per_sm));
     tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
 }
 
