@@ -230,6 +230,13 @@ VM_API vm_status vm_stage_times(vm_engine* engine, const char** names, float* mi
 VM_API vm_status vm_timer_start(vm_engine* engine);
 VM_API vm_status vm_timer_stop(vm_engine* engine, float* milliseconds);
 
+/* No counterpart in the reference. Every wait of one thread block on another agent inside the tensor-core kernels (an
+ * mbarrier armed by the tensor core or by another warp) polls at most `polls` times, then the kernel raises its abort
+ * flag, leaves through its normal tear-down and the call returns VM_ERR_DEVICE_ABORT with the engine still usable.
+ * The default (4,000,000 polls, a few seconds) is never reached by a healthy run. 0 makes every such wait give up at
+ * once: the way to exercise the error path without hanging or faulting the device. */
+VM_API vm_status vm_set_wait_limit(vm_engine* engine, uint32_t polls);
+
 /* Number of kernels launched by this engine since creation. */
 VM_API int64_t vm_launch_count(const vm_engine* engine);
 

@@ -149,9 +149,71 @@ def make_units(seed=99):
     np.savez_compressed(os.path.join(HERE, "units.npz"), **out)
 
 
+def make_example_model_case(reference, name="example_model_ring6_rectilinear_rgba", indices=(0, 10, 20), scale=2):
+    """The reference's own trained network (example/model.yaml: 13 groups, 28x16 ... 56x5, read as
+    example/load_model.hpp:25-52 reads it) on three of its example frames (example/images/imageNNNNNNN.jpg with the
+    lens and Hoc of lensNNNNNNN.yaml), through the reference CPU engine. The frames are stored decoded (JPEG decoders
+    differ in their last bits) at 1/scale of their resolution, with the focal length scaled to match, to keep the
+    fixture small; the mesh is the benchmark's Ring6 over the model's sphere (example/benchmark.cpp:121-122) at the
+    first frame's camera height with fewer intersections and a shorter range. Mesh tables are not stored: the engine's own
+    host mesh builder reproduces them (their digest is stored and checked)."""
+    import hashlib
+
+    import yaml
+    from PIL import Image
+
+    from visualmesh_b200 import model_io
+    example = os.path.join(reference, "example")
+    net, mesh_name, geometry = model_io.load_model(os.path.join(example, "model.yaml"))
+    assert mesh_name == "RING6"
+    docs = [yaml.safe_load(open(os.path.join(example, "images", f"lens{i:07d}.yaml"))) for i in indices]
+    # the frames' camera heights differ slightly (1.07 .. 1.2 m); like a table entry of the benchmark's VisualMesh, one
+    # Mesh (at the first frame's height) serves them all - the Mesh overload of the engines takes the mesh it is given
+    spec = W.MeshSpec("RING6", "SPHERE", float(geometry["radius"]), 0.0, float(docs[0]["Hoc"][2][3]), 4.0, 10.0)
+    mesh = R.RefMesh(spec)
+    rays, nbrs = mesh.nodes()
+    digest = hashlib.sha256(rays.tobytes() + nbrs.tobytes()).hexdigest()
+    first = Image.open(os.path.join(example, "images", f"image{indices[0]:07d}.jpg"))
+    Wd, Ht = first.size[0] // scale, first.size[1] // scale
+    proj = {"RECTILINEAR": W.RECTILINEAR, "EQUISOLID": W.EQUISOLID, "EQUIDISTANT": W.EQUIDISTANT}
+    fmt = W.fourcc("RGBA")
+    out = dict(format=np.uint32(fmt), n_frames=np.int32(len(indices)), mesh_digest=np.array(digest),
+               mesh_spec=np.array([spec.model, spec.shape, repr(spec.shape_a), repr(spec.shape_b), repr(spec.h),
+                                   repr(spec.k), repr(spec.max_distance)]),
+               source=np.array([f"example/images/image{i:07d}.jpg" for i in indices]))
+    out.update(net_arrays(net))
+    for f, (i, doc) in enumerate(zip(indices, docs)):
+        img = Image.open(os.path.join(example, "images", f"image{i:07d}.jpg")).convert("RGB")
+        rgb = np.asarray(img.resize((Wd, Ht), Image.BILINEAR), dtype=np.uint8)
+        rgba = np.concatenate([rgb, np.full((Ht, Wd, 1), 255, np.uint8)], axis=2).reshape(-1)
+        focal = float(doc["focal_length"]) / scale
+        fov = float(doc.get("fov", 2.0 * math.atan(math.hypot(Wd, Ht) * 0.5 / focal)))
+        k = [float(v) for v in doc.get("k", (0.0, 0.0))]
+        # k applies to radii in pixels (cpp/visualmesh/utility/projection.hpp:163-176): r' = r / scale
+        lens = W.Lens((Wd, Ht), proj[doc["projection"]], focal, tuple(float(v) / scale for v in doc.get("centre", (0, 0))),
+                      (k[0] * scale**2, k[1] * scale**4), fov)
+        Hoc = np.asarray(doc["Hoc"], dtype=np.float32).reshape(4, 4)
+        c = mesh.classify(net, Hoc, lens, rgba, fmt)
+        out[f"f{f}_lens"] = np.array([Wd, Ht, lens.projection, lens.focal_length, lens.centre[0], lens.centre[1],
+                                      lens.k[0], lens.k[1], lens.fov], np.float64)
+        out[f"f{f}_Hoc"] = Hoc
+        out[f"f{f}_rgb"] = rgb
+        out[f"f{f}_ranges"] = mesh.lookup(Hoc, lens)
+        out[f"f{f}_px"] = c["pixel_coordinates"]
+        out[f"f{f}_gi"] = c["global_indices"]
+        out[f"f{f}_nb"] = c["neighbourhood"]
+        out[f"f{f}_cls"] = c["classifications"]
+        print(name, f, "nodes", mesh.n_nodes, "on screen", len(c["global_indices"]),
+              "classes argmax histogram", np.bincount(c["classifications"][:-1].argmax(1), minlength=5))
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
+
+
 if __name__ == "__main__":
-    for case in CASES:
-        make_case(*case)
-    make_units()
+    reference = os.environ.get("VM_REFERENCE", "/root/reference")
+    if "--example-model-only" not in sys.argv:
+        for case in CASES:
+            make_case(*case)
+        make_units()
+    make_example_model_case(reference)
     total = sum(os.path.getsize(os.path.join(HERE, f)) for f in os.listdir(HERE) if f.endswith(".npz"))
     print("total fixture bytes", total)

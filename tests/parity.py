@@ -97,3 +97,83 @@ def compare(out, ref, dims) -> Report:
             rep.cls_over_tol = int((dc > TOL_CLS).sum())
             rep.cls_entries = int(dc.size)
     return rep
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Whole configurations: every frame through the compiled reference CPU engine and through the CUDA engine
+# ---------------------------------------------------------------------------------------------------------------------
+
+def config_parity(cfg, n_frames=None, seed=0, threads=None, batch_frames=16, engine=None):
+    """Runs the first n_frames of benchmark configuration `cfg` (all of them when None) through the reference CPU
+    engine (oracle/_ref/libvmref.so: a fresh cpu::Engine per frame, `threads` frames at a time) and through the CUDA
+    engine (device-side lookup, host images, batches of `batch_frames`), and compares frame by frame under the
+    tolerances at the top of this file. Returns a dict:
+
+        frames, frames_ok          frames compared / frames with every entry within tolerance
+        nodes                      on-screen nodes over all frames (reference)
+        indices_exact_frames       frames whose global_indices and neighbourhood are bit-exact
+        border_nodes, stray_nodes  nodes on one side only: within 1e-3 px of the border (allowed, reported) / not (failure)
+        max_px, px_bit_identical   largest pixel difference; fraction of coordinates with identical bits
+        max_cls, cls_over_tol, cls_entries
+        reference_seconds          wall time of the reference runs
+    """
+    import os
+    import time
+    from concurrent.futures import ThreadPoolExecutor
+
+    import refharness as R
+    from visualmesh_b200 import workloads as W
+    from visualmesh_b200.engine import Engine, FrameInput, Mesh
+
+    wl = W.config(cfg, seed=seed, n_frames=n_frames)
+    threads = threads or os.cpu_count() or 1
+    own_engine = engine is None
+    if own_engine:
+        engine = Engine(wl.network)
+    ref_meshes, meshes = {}, {}
+    for fr in wl.frames:
+        if fr.mesh.key() not in ref_meshes:
+            ref_meshes[fr.mesh.key()] = R.RefMesh(fr.mesh)
+            meshes[fr.mesh.key()] = Mesh.from_spec(fr.mesh)
+
+    total = dict(frames=0, frames_ok=0, nodes=0, indices_exact_frames=0, border_nodes=0, stray_nodes=0, max_px=0.0,
+                 max_cls=0.0, cls_over_tol=0, cls_entries=0, reference_seconds=0.0)
+    px_same, px_count = 0.0, 0
+    # a window of frames at a time bounds the memory held (a config-3 frame and its results are ~150 MB)
+    window = max(batch_frames, threads)
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        for w0 in range(0, len(wl.frames), window):
+            frames = wl.frames[w0:w0 + window]
+            images = [fr.image() for fr in frames]
+            t0 = time.perf_counter()
+            refs = list(pool.map(lambda a: ref_meshes[a[0].mesh.key()].classify(wl.network, a[0].Hoc, a[0].lens, a[1],
+                                                                                a[0].format), zip(frames, images)))
+            total["reference_seconds"] += time.perf_counter() - t0
+            for b0 in range(0, len(frames), batch_frames):
+                part = range(b0, min(b0 + batch_frames, len(frames)))
+                batch = engine.run_batch([FrameInput(meshes[frames[i].mesh.key()], frames[i].Hoc, frames[i].lens,
+                                                     images[i], frames[i].format, None) for i in part])
+                for j, i in enumerate(part):
+                    rep = compare(batch.frame(j, copy=False), refs[i], frames[i].lens.dimensions)
+                    total["frames"] += 1
+                    total["frames_ok"] += int(rep.ok and (rep.n_ref == rep.n_out or bool(rep.border_nodes)))
+                    total["nodes"] += rep.n_ref
+                    total["indices_exact_frames"] += int(rep.indices_exact and rep.neighbourhood_exact)
+                    total["border_nodes"] += len(rep.border_nodes)
+                    total["stray_nodes"] += len(rep.stray_nodes)
+                    total["max_px"] = max(total["max_px"], rep.max_px)
+                    total["max_cls"] = max(total["max_cls"], rep.max_cls)
+                    total["cls_over_tol"] += rep.cls_over_tol
+                    total["cls_entries"] += rep.cls_entries
+                    px_same += rep.px_bit_identical * 2 * rep.n_ref
+                    px_count += 2 * rep.n_ref
+    total["px_bit_identical"] = px_same / px_count if px_count else 1.0
+    total["pass"] = f"{total['frames_ok']}/{total['frames']}"
+    if own_engine:
+        engine.close()
+    return total
+
+
+# frames per configuration that "every frame" means: the configurations' own counts, and a 256-frame prefix of the
+# 4096-frame stream of configuration 4 (all four camera heights occur in it)
+FULL_PARITY_FRAMES = {0: 1, 1: 64, 2: 32, 3: 32, 4: 256}

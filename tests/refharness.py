@@ -2,7 +2,9 @@
 
 Test infrastructure only. The library is built by oracle/Makefile from the reference's headers; where it has not
 been built (no reference checkout on this machine and no prebuilt file) `available()` is False and tests that need
-it skip.
+it skip. libvmref.so holds reference code only. A second build of the same harness, libvmref_cuda.so, also carries
+the C++ drop-in engine (include/visualmesh/engine/cuda/engine.hpp) and therefore links the CUDA library; it is loaded
+only by the tests that call the drop-in (`classify(cuda=True)`), never by the timed CPU baseline.
 """
 import ctypes as C
 import os
@@ -11,6 +13,7 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "..", "oracle", "_ref", "libvmref.so")
+_CUDA_LIB_PATH = os.path.join(_HERE, "..", "oracle", "_ref", "libvmref_cuda.so")
 
 
 class CLens(C.Structure):
@@ -63,87 +66,106 @@ def c_network(network):
 
 
 _lib = None
+_cuda_lib = None
 
 
 def available() -> bool:
     return os.path.exists(_LIB_PATH)
 
 
+def drop_in_available() -> bool:
+    return os.path.exists(_CUDA_LIB_PATH)
+
+
+def cuda_lib():
+    """The harness build that also carries the C++ drop-in CUDA engine. Meshes are created by the library that uses
+    them: a RefMesh made with cuda=True lives in this one."""
+    global _cuda_lib
+    if _cuda_lib is None:
+        _cuda_lib = _declare(C.CDLL(_CUDA_LIB_PATH))
+    return _cuda_lib
+
+
 def lib():
     global _lib
     if _lib is None:
-        l = C.CDLL(_LIB_PATH)
-        l.vmref_last_error.restype = C.c_char_p
-        l.vmref_mesh_create.restype = C.c_void_p
-        l.vmref_mesh_create.argtypes = [C.c_char_p, C.c_char_p] + [C.c_float] * 5
-        l.vmref_mesh_destroy.argtypes = [C.c_void_p]
-        for name in ("vmref_mesh_n_nodes", "vmref_mesh_n_neighbours", "vmref_mesh_n_bsp"):
-            getattr(l, name).argtypes = [C.c_void_p]
-            getattr(l, name).restype = C.c_int
-        l.vmref_mesh_nodes.argtypes = [C.c_void_p] * 3
-        l.vmref_mesh_bsp.argtypes = [C.c_void_p] * 4
-        l.vmref_mesh_lookup.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(CLens), C.c_void_p, C.c_int]
-        l.vmref_project.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(CLens), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
-        l.vmref_classify.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(CLens), C.c_void_p, C.c_uint32,
-                                     C.POINTER(CLayer), C.POINTER(C.c_int32), C.c_int,
-                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
-                                     C.POINTER(C.c_int)]
-        if hasattr(l, "vmref_cuda_classify"):
-            l.vmref_cuda_classify.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(CLens), C.c_void_p, C.c_uint32,
-                                              C.POINTER(CLayer), C.POINTER(C.c_int32), C.c_int, C.c_int,
-                                              C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
-                                              C.POINTER(C.c_int)]
-        l.vmref_project_rays.argtypes = [C.c_void_p, C.c_int, C.POINTER(CLens), C.c_void_p]
-        l.vmref_interpolate.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_void_p]
-        l.vmref_run_stream.restype = C.c_double
-        l.vmref_run_stream.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
-                                       C.POINTER(CLayer), C.POINTER(C.c_int32), C.c_int, C.c_int,
-                                       C.POINTER(C.c_longlong)]
-        _lib = l
+        _lib = _declare(C.CDLL(_LIB_PATH))
     return _lib
 
 
-class RefMesh:
-    """visualmesh::Mesh<float, Model> of the reference."""
+def _declare(l):
+    l.vmref_last_error.restype = C.c_char_p
+    l.vmref_mesh_create.restype = C.c_void_p
+    l.vmref_mesh_create.argtypes = [C.c_char_p, C.c_char_p] + [C.c_float] * 5
+    l.vmref_mesh_destroy.argtypes = [C.c_void_p]
+    for name in ("vmref_mesh_n_nodes", "vmref_mesh_n_neighbours", "vmref_mesh_n_bsp"):
+        getattr(l, name).argtypes = [C.c_void_p]
+        getattr(l, name).restype = C.c_int
+    l.vmref_mesh_nodes.argtypes = [C.c_void_p] * 3
+    l.vmref_mesh_bsp.argtypes = [C.c_void_p] * 4
+    l.vmref_mesh_lookup.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(CLens), C.c_void_p, C.c_int]
+    l.vmref_project.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(CLens), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+    l.vmref_classify.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(CLens), C.c_void_p, C.c_uint32,
+                                 C.POINTER(CLayer), C.POINTER(C.c_int32), C.c_int,
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                 C.POINTER(C.c_int)]
+    if hasattr(l, "vmref_cuda_classify"):
+        l.vmref_cuda_classify.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(CLens), C.c_void_p, C.c_uint32,
+                                          C.POINTER(CLayer), C.POINTER(C.c_int32), C.c_int, C.c_int,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                          C.POINTER(C.c_int)]
+    l.vmref_project_rays.argtypes = [C.c_void_p, C.c_int, C.POINTER(CLens), C.c_void_p]
+    l.vmref_interpolate.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_uint32, C.c_void_p]
+    l.vmref_run_stream.restype = C.c_double
+    l.vmref_run_stream.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                   C.POINTER(CLayer), C.POINTER(C.c_int32), C.c_int, C.c_int,
+                                   C.POINTER(C.c_longlong)]
+    return l
 
-    def __init__(self, spec):
+
+class RefMesh:
+    """visualmesh::Mesh<float, Model> of the reference. with_drop_in=True builds it inside the harness that also
+    carries the C++ drop-in CUDA engine, so that both engines can be called on this one object."""
+
+    def __init__(self, spec, with_drop_in=False):
         self.spec = spec
-        self.ptr = lib().vmref_mesh_create(spec.model.encode(), spec.shape.encode(), spec.shape_a, spec.shape_b,
+        self._l = cuda_lib() if with_drop_in else lib()
+        self.ptr = self._l.vmref_mesh_create(spec.model.encode(), spec.shape.encode(), spec.shape_a, spec.shape_b,
                                            spec.h, spec.k, spec.max_distance)
         if not self.ptr:
-            raise RuntimeError(lib().vmref_last_error().decode())
-        self.n_nodes = lib().vmref_mesh_n_nodes(self.ptr)
-        self.n_neighbours = lib().vmref_mesh_n_neighbours(self.ptr)
+            raise RuntimeError(self._l.vmref_last_error().decode())
+        self.n_nodes = self._l.vmref_mesh_n_nodes(self.ptr)
+        self.n_neighbours = self._l.vmref_mesh_n_neighbours(self.ptr)
         self._nodes = None
 
     def __del__(self):
         if getattr(self, "ptr", None):
-            lib().vmref_mesh_destroy(self.ptr)
+            self._l.vmref_mesh_destroy(self.ptr)
             self.ptr = None
 
     def nodes(self):
         if self._nodes is None:
             rays = np.empty((self.n_nodes, 3), dtype=np.float32)
             nbrs = np.empty((self.n_nodes, self.n_neighbours), dtype=np.int32)
-            lib().vmref_mesh_nodes(self.ptr, rays.ctypes.data, nbrs.ctypes.data)
+            self._l.vmref_mesh_nodes(self.ptr, rays.ctypes.data, nbrs.ctypes.data)
             self._nodes = (rays, nbrs)
         return self._nodes
 
     def bsp(self):
-        n = lib().vmref_mesh_n_bsp(self.ptr)
+        n = self._l.vmref_mesh_n_bsp(self.ptr)
         ranges = np.empty((n, 2), dtype=np.int32)
         children = np.empty((n, 2), dtype=np.int32)
         cones = np.empty((n, 5), dtype=np.float32)
-        lib().vmref_mesh_bsp(self.ptr, ranges.ctypes.data, children.ctypes.data, cones.ctypes.data)
+        self._l.vmref_mesh_bsp(self.ptr, ranges.ctypes.data, children.ctypes.data, cones.ctypes.data)
         return ranges, children, cones
 
     def lookup(self, Hoc, lens):
         Hoc = np.ascontiguousarray(Hoc, dtype=np.float32)
         cap = 1 << 16
         ranges = np.empty((cap, 2), dtype=np.int32)
-        n = lib().vmref_mesh_lookup(self.ptr, Hoc.ctypes.data, C.byref(c_lens(lens)), ranges.ctypes.data, cap)
+        n = self._l.vmref_mesh_lookup(self.ptr, Hoc.ctypes.data, C.byref(c_lens(lens)), ranges.ctypes.data, cap)
         if n < 0:
-            raise RuntimeError(lib().vmref_last_error().decode())
+            raise RuntimeError(self._l.vmref_last_error().decode())
         assert n <= cap
         return ranges[:n].copy()
 
@@ -158,10 +180,10 @@ class RefMesh:
     def project(self, Hoc, lens):
         Hoc = np.ascontiguousarray(Hoc, dtype=np.float32)
         cap, px, nb, gi, _ = self._outputs(0)
-        n = lib().vmref_project(self.ptr, Hoc.ctypes.data, C.byref(c_lens(lens)), px.ctypes.data, nb.ctypes.data,
+        n = self._l.vmref_project(self.ptr, Hoc.ctypes.data, C.byref(c_lens(lens)), px.ctypes.data, nb.ctypes.data,
                                 gi.ctypes.data, cap)
         if n < 0:
-            raise RuntimeError(lib().vmref_last_error().decode())
+            raise RuntimeError(self._l.vmref_last_error().decode())
         return dict(pixel_coordinates=px[:n].copy(), neighbourhood=nb[:n + 1].copy(), global_indices=gi[:n].copy())
 
     def classify(self, network, Hoc, lens, image, fmt, cuda=False, project_only=False):
@@ -173,15 +195,15 @@ class RefMesh:
         cap, px, nb, gi, cl = self._outputs(n_out)
         ncls = C.c_int(0)
         if cuda:
-            n = lib().vmref_cuda_classify(self.ptr, Hoc.ctypes.data, C.byref(c_lens(lens)), image.ctypes.data, fmt,
+            n = self._l.vmref_cuda_classify(self.ptr, Hoc.ctypes.data, C.byref(c_lens(lens)), image.ctypes.data, fmt,
                                           layers, lpg, n_groups, int(project_only), px.ctypes.data, nb.ctypes.data,
                                           gi.ctypes.data, cl.ctypes.data, cap, cl.size, C.byref(ncls))
         else:
-            n = lib().vmref_classify(self.ptr, Hoc.ctypes.data, C.byref(c_lens(lens)), image.ctypes.data, fmt,
+            n = self._l.vmref_classify(self.ptr, Hoc.ctypes.data, C.byref(c_lens(lens)), image.ctypes.data, fmt,
                                      layers, lpg, n_groups, px.ctypes.data, nb.ctypes.data, gi.ctypes.data,
                                      cl.ctypes.data, cap, cl.size, C.byref(ncls))
         if n < 0:
-            raise RuntimeError(lib().vmref_last_error().decode())
+            raise RuntimeError(self._l.vmref_last_error().decode())
         k = ncls.value
         if n == 0:
             return dict(pixel_coordinates=px[:0], neighbourhood=nb[:0], global_indices=gi[:0],

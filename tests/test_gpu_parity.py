@@ -182,7 +182,9 @@ def _check_config(cfg, n_frames, via_cpp):
     engine = Engine(wl.network)
     frames_ok = 0
     for f, fr in enumerate(wl.frames):
-        ref_mesh = ref_meshes.setdefault(fr.mesh.key(), R.RefMesh(fr.mesh))
+        if fr.mesh.key() not in ref_meshes:
+            ref_meshes[fr.mesh.key()] = R.RefMesh(fr.mesh, with_drop_in=via_cpp)
+        ref_mesh = ref_meshes[fr.mesh.key()]
         image = fr.image()
         ref = ref_mesh.classify(wl.network, fr.Hoc, fr.lens, image, fr.format)
         if via_cpp:
@@ -209,15 +211,8 @@ def test_benchmark_config_vs_compiled_reference(cfg, n_frames):
     _check_config(cfg, n_frames, via_cpp=False)
 
 
-def _harness_has_drop_in():
-    try:
-        return R.available() and hasattr(R.lib(), "vmref_cuda_classify")
-    except OSError:
-        return False
-
-
 @needs_ref
-@pytest.mark.skipif(not _harness_has_drop_in(), reason="harness built without the CUDA drop-in")
+@pytest.mark.skipif(not R.drop_in_available(), reason="harness with the CUDA drop-in (oracle/_ref/libvmref_cuda.so) not present")
 @pytest.mark.parametrize("cfg,n_frames", [(0, 1), (2, 2)])
 def test_cpp_drop_in_engine_vs_cpu_engine_on_the_same_mesh_object(cfg, n_frames):
     _check_config(cfg, n_frames, via_cpp=True)
@@ -256,6 +251,42 @@ def test_config3_dense_mesh_through_the_tensor_core_layers():
     print(f"cfg3 (4 layers, tcgen05): {rep}")
     assert rep.ok and rep.n_ref > 900000, str(rep)
     engine.close()
+
+
+# ---- the reference's own trained model on its own example frames ----------------------------------------------------
+
+@pytest.mark.parametrize("lookup", ["host_ranges", "device_lookup"])
+def test_example_model_on_example_frames(lookup):
+    """example/model.yaml (13 groups, 28x16 ... 56x5 softmax, trained weights) on three frames of example/images,
+    against the stored outputs of the reference CPU engine - the whole call through the C ABI."""
+    case = G.ExampleModelCase()
+    mesh = Mesh.from_spec(case.mesh_spec)
+    case.check_mesh(mesh.rays, mesh.neighbours)
+    engine = Engine(case.network)
+    frames = [FrameInput(mesh, fr["Hoc"], fr["lens"], fr["image"], case.format,
+                         fr["ranges"] if lookup == "host_ranges" else None) for fr in case.frames]
+    singles = [engine.run_batch([f]).frame(0) for f in frames]
+    batch = engine.run_batch(frames)
+    for f, fr in enumerate(case.frames):
+        rep = P.compare(singles[f], fr, fr["lens"].dimensions)
+        print(f"example model frame {f} {lookup}: {rep}")
+        assert rep.ok and rep.indices_exact and rep.n_ref > 1000, str(rep)
+        assert rep.px_bit_identical > 0.999, str(rep)
+        assert np.array_equal(G.bits(batch.frame(f).classifications), G.bits(singles[f].classifications))
+    engine.close()
+
+
+@pytest.mark.skipif(not R.drop_in_available(), reason="harness with the CUDA drop-in (oracle/_ref/libvmref_cuda.so) not present")
+def test_example_model_through_the_cpp_drop_in_engine():
+    """The same case through visualmesh::engine::cuda::Engine<float> on a reference Mesh object."""
+    case = G.ExampleModelCase()
+    ref_mesh = R.RefMesh(case.mesh_spec, with_drop_in=True)
+    case.check_mesh(*ref_mesh.nodes())
+    for f, fr in enumerate(case.frames):
+        out = ref_mesh.classify(case.network, fr["Hoc"], fr["lens"], fr["image"], case.format, cuda=True)
+        rep = P.compare(out, fr, fr["lens"].dimensions)
+        print(f"example model frame {f} c++ drop-in: {rep}")
+        assert rep.ok and rep.indices_exact, str(rep)
 
 
 # ---- tensor-core graph convolution (tcgen05) ---------------------------------------------------------------------------

@@ -12,7 +12,7 @@ import refharness as R
 from visualmesh_b200 import model_io
 from visualmesh_b200 import workloads as W
 
-EXAMPLE = "/root/reference/example"
+EXAMPLE = os.path.join(os.environ.get("VM_REFERENCE", "/root/reference"), "example")
 
 
 def test_round_trip_and_shape_checks(tmp_path):
@@ -63,3 +63,22 @@ def test_reference_example_model_and_frame_pin_the_oracle():
     assert len(ref["global_indices"]) > 100
     for key in ref:
         assert np.array_equal(G.bits(out[key]), G.bits(ref[key])), key
+
+
+def test_example_model_fixture_pins_the_oracle_and_the_host_mesh_builder():
+    """The stored outputs of the reference CPU engine for its own trained network on three of its example frames:
+    the engine's host mesh builder reproduces the mesh, its host lookup the ranges, and the plain-C oracle every output
+    array, bit for bit - on any machine, without the reference checkout."""
+    from visualmesh_b200.engine import Mesh
+    case = G.ExampleModelCase()
+    assert len(case.network) == 13 and case.network[0][0].weights.shape == (28, 16)
+    assert case.network[-1][0].weights.shape == (56, 5) and case.network[-1][0].activation == W.SOFTMAX
+    mesh = Mesh.from_spec(case.mesh_spec)
+    case.check_mesh(mesh.rays, mesh.neighbours)
+    for fr in case.frames:
+        ranges = mesh.lookup(fr["Hoc"], fr["lens"])
+        assert np.array_equal(ranges, fr["ranges"])
+        out = O.classify(mesh.rays, mesh.neighbours, ranges, case.network, fr["Hoc"], fr["lens"], fr["image"], case.format)
+        assert len(out["global_indices"]) > 1000
+        for key in ("global_indices", "neighbourhood", "pixel_coordinates", "classifications"):
+            assert np.array_equal(G.bits(out[key]), G.bits(fr[key])), key

@@ -39,6 +39,12 @@ def _static_call(engine, mesh, Hoc, lens, n_nodes, N):
     return px[:k].cpu().numpy(), gi[:k].cpu().numpy(), nb[:k + 1].cpu().numpy(), gi[k:].cpu().numpy()
 
 
+def _free_device_bytes():
+    import torch
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]
+
+
 def test_static_projection_matches_the_allocating_entry_point_twice_in_a_row():
     case = G.Case("ring6_equisolid_rgba")
     engine = Engine()  # projection only
@@ -54,6 +60,37 @@ def test_static_projection_matches_the_allocating_entry_point_twice_in_a_row():
         assert np.all(untouched == -7), "entries past n must be left alone"
         # and both agree with the reference fixture on the on-screen set and the neighbourhood
         assert np.array_equal(gi, fr["global_indices"]) and np.array_equal(nb, fr["neighbourhood"])
+    engine.close()
+
+
+def test_static_projection_allocates_no_device_memory():
+    """The property the entry point exists for: with the caller's output buffers in place, the free device memory is
+    the same before and after the second and the third call (the first call of a process may load the library's
+    kernels, which is why set-up should make it)."""
+    import torch
+    case = G.Case("ring6_equisolid_rgba")
+    engine = Engine()
+    mesh = Mesh.from_arrays(case.rays, case.nbrs, case.bsp)
+    n_nodes, N = case.nbrs.shape
+    handle = engine._device_mesh(mesh)
+    px = torch.empty((n_nodes, 2), dtype=torch.float32, device="cuda")
+    gi = torch.empty((n_nodes,), dtype=torch.int32, device="cuda")
+    nb = torch.empty((n_nodes + 1, N), dtype=torch.int32, device="cuda")
+    lens = _c_lens(case.lens)
+    lib = abi.load()
+
+    def call(fr):
+        H = np.ascontiguousarray(fr["Hoc"], dtype=np.float32)
+        n = C.c_int32(-1)
+        abi.check(lib.vm_project_static(engine._ptr, handle, H.ctypes.data, C.byref(lens), px.data_ptr(), gi.data_ptr(),
+                                        nb.data_ptr(), None, C.byref(n)))
+        return n.value
+
+    assert call(case.frames[0]) == len(case.frames[0]["global_indices"])
+    free = _free_device_bytes()
+    for fr in (case.frames[1], case.frames[2]):
+        assert call(fr) == len(fr["global_indices"])
+        assert _free_device_bytes() == free, "vm_project_static changed the amount of free device memory"
     engine.close()
 
 
@@ -80,4 +117,18 @@ def test_static_projection_rejects_what_does_not_fit():
     status = lib.vm_project_static(engine._ptr, engine._device_mesh(small), H.ctypes.data, C.byref(_c_lens(case.lens)),
                                    dummy, dummy, dummy, None, None)
     assert status == abi.VM_ERR_NO_BSP
+    # a mesh that was uploaded through another engine is refused
+    other = Engine()
+    foreign = other._device_mesh(Mesh.from_arrays(case.rays, case.nbrs, case.bsp))
+    status = lib.vm_project_static(engine._ptr, foreign, H.ctypes.data, C.byref(_c_lens(case.lens)), dummy, dummy, dummy,
+                                   None, None)
+    assert status == abi.VM_ERR_INVALID_ARGUMENT and b"another engine" in lib.vm_last_error()
+    # and so are lens dimensions that are not positive
+    bad = _c_lens(case.lens)
+    bad.dimensions[0] = 0
+    status = lib.vm_project_static(engine._ptr, engine._device_mesh(Mesh.from_arrays(case.rays, case.nbrs, case.bsp)),
+                                   H.ctypes.data, C.byref(bad), dummy, dummy, dummy, None, None)
+    assert status == abi.VM_ERR_INVALID_ARGUMENT
+    assert lib.vm_launch_count(engine._ptr) == n
+    other.close()
     engine.close()

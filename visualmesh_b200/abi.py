@@ -87,6 +87,7 @@ SYMBOLS = {
                                  C.POINTER(C.c_int32)]),
     "vm_timer_start": (C.c_int, [C.c_void_p]),
     "vm_timer_stop": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
+    "vm_set_wait_limit": (C.c_int, [C.c_void_p, C.c_uint32]),
     "vm_launch_count": (C.c_int64, [C.c_void_p]),
     "vm_host_alloc": (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
     "vm_host_free": (None, [C.c_void_p]),

@@ -28,7 +28,7 @@ namespace tc {
 
     constexpr int TILE_ROWS     = 128;
     constexpr int MAX_FRAMES    = 64;       // frames per launch whose tile counts fit the shared prefix table
-    constexpr uint32_t WAIT_LIMIT = 4000000;  // polls of mbarrier.try_wait before giving up
+    constexpr uint32_t WAIT_LIMIT = 4000000;  // default polls of mbarrier.try_wait before giving up (Args::wait_limit)
     constexpr int ABORT_TC_TIMEOUT = 2;
 
     __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -51,8 +51,8 @@ namespace tc {
         return ok != 0;
     }
     // false when the limit ran out
-    __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-        for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit) {
+        for (uint32_t i = 0; i < limit; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
         }
         return false;
@@ -85,6 +85,7 @@ namespace tc {
         int32_t n_frames;
         int32_t cout;
         int32_t* abort_flag;
+        uint32_t wait_limit;  // polls of one mbarrier wait before the kernel gives up (0: every wait fails at once)
     };
 
     constexpr int ABORT_TC_RANGE = ABORT_RANGE;  // a feature value too large for the fp16 split: the host falls back to FFMA
@@ -126,8 +127,8 @@ namespace tc {
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
     }
     // bounded wait that also gives up as soon as another role of the CTA has failed
-    __device__ __forceinline__ bool mbar_wait_or_fail(uint32_t bar, uint32_t parity, volatile int32_t* failed) {
-        for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    __device__ __forceinline__ bool mbar_wait_or_fail(uint32_t bar, uint32_t parity, volatile int32_t* failed, uint32_t limit) {
+        for (uint32_t i = 0; i < limit; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
             if ((i & 1023u) == 1023u && *failed) return false;
         }
@@ -157,8 +158,8 @@ namespace tc {
         constexpr int DEPTH      = CIN <= 16 ? 2 : 1;    // slots whose loads are in flight ahead of the one being stored
 
         extern __shared__ __align__(1024) unsigned char smem_raw[];
-        // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
-        __shared__ uint64_t bars[2 * STAGES + 4];
+        // full[STAGES], empty[STAGES], acc_full[2], acc_empty[2], drain
+        __shared__ uint64_t bars[2 * STAGES + 5];
         __shared__ uint32_t tmem_base_slot;
         __shared__ int32_t tile_prefix[MAX_FRAMES + 1];
         __shared__ int32_t failed_s;
@@ -173,6 +174,7 @@ namespace tc {
         const uint32_t bar_empty     = smem_u32(&bars[STAGES]);
         const uint32_t bar_acc_full  = smem_u32(&bars[2 * STAGES]);
         const uint32_t bar_acc_empty = smem_u32(&bars[2 * STAGES + 2]);
+        const uint32_t bar_drain     = smem_u32(&bars[2 * STAGES + 4]);
 
         // ---- set-up ----
         if (tid == 0) {
@@ -185,6 +187,7 @@ namespace tc {
                 mbar_init(bar_acc_full + 8 * i, 1);
                 mbar_init(bar_acc_empty + 8 * i, PRODUCER_WARPS);
             }
+            mbar_init(bar_drain, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             int run = 0;
             for (int f = 0; f < t.n_frames; ++f) {
@@ -227,14 +230,14 @@ namespace tc {
                     const uint32_t ab  = tile_count & 1u;
                     const uint32_t acc = tmem_base + ab * (2 * NP);
                     // the epilogue of the tile that used this accumulator two tiles ago must have read it
-                    if (tile_count >= 2 && !mbar_wait_or_fail(bar_acc_empty + 8 * ab, ((tile_count >> 1) - 1) & 1u, failed)) {
+                    if (tile_count >= 2 && !mbar_wait_or_fail(bar_acc_empty + 8 * ab, ((tile_count >> 1) - 1) & 1u, failed, t.wait_limit)) {
                         ok = false;
                         break;
                     }
                     for (int s = 0; s < NSLOTS; ++s, ++it) {
                         const uint32_t stage = it % STAGES;
                         const uint32_t use   = it / STAGES;
-                        if (!mbar_wait_or_fail(bar_full + 8 * stage, use & 1u, failed)) {
+                        if (!mbar_wait_or_fail(bar_full + 8 * stage, use & 1u, failed, t.wait_limit)) {
                             ok = false;
                             break;
                         }
@@ -253,7 +256,16 @@ namespace tc {
                         if (s == NSLOTS - 1) commit(bar_acc_full + 8 * ab);
                     }
                 }
-                if (!ok) failed_s = 1;
+                if (!ok) {
+                    failed_s = 1;
+                    // Giving up: MMAs issued so far may still be running against this CTA's tensor memory and stages.
+                    // One more commit tracks them all; the tear-down below frees the tensor memory only after it (the
+                    // wait uses the full default limit whatever the kernel was told, and is itself bounded).
+                    if (it > 0) {
+                        commit(bar_drain);
+                        mbar_wait(bar_drain, 0u, WAIT_LIMIT);
+                    }
+                }
             }
         }
         else {
@@ -301,10 +313,16 @@ namespace tc {
                         for (int c = 0; c < CIN / 4; ++c) ring[s % DEPTH][c] = in4[static_cast<size_t>(c) * a.in_stride + src_rows[s + DEPTH]];
                     }
                     // the MMAs that read this stage on its previous use must be done
-                    if (use > 0 && !mbar_wait_or_fail(bar_empty + 8 * stage, (use - 1) & 1u, failed)) ok = false;
+                    if (use > 0 && !mbar_wait_or_fail(bar_empty + 8 * stage, (use - 1) & 1u, failed, t.wait_limit)) {
+                        ok      = false;
+                        *failed = 1;
+                    }
                     unsigned char* hi_p = stage_base + static_cast<size_t>(stage) * 2 * SLOT_BYTES;
                     unsigned char* lo_p = hi_p + SLOT_BYTES;
-                    if (HALF) {
+                    if (!ok) {
+                        // the stage may still be read by the tensor core: nothing is written into it any more
+                    }
+                    else if (HALF) {
 #pragma unroll
                         for (int p = 0; p < PLANES; ++p) {
                             const float x[8] = {cur[2 * p].x, cur[2 * p].y, cur[2 * p].z, cur[2 * p].w,
@@ -351,7 +369,7 @@ namespace tc {
 
                 // ---- epilogue: accumulator -> registers -> bias, activation -> global ----
                 // the tensor-memory load is warp-collective: the warp decides together whether to go on
-                const bool arrived = mbar_wait_or_fail(bar_acc_full + 8 * ab, (tile_count >> 1) & 1u, failed);
+                const bool arrived = mbar_wait_or_fail(bar_acc_full + 8 * ab, (tile_count >> 1) & 1u, failed, t.wait_limit);
                 ok                 = __all_sync(0xffffffffu, arrived);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -499,7 +517,7 @@ namespace tc {
         static_assert(DEPTH == 2 || DEPTH == 3, "the tile loop below is written out for two or three phases");
 
         extern __shared__ __align__(1024) unsigned char smem_raw[];
-        __shared__ uint64_t bars[2 * STAGES + 4];
+        __shared__ uint64_t bars[2 * STAGES + 5];
         __shared__ uint32_t tmem_base_slot;
         __shared__ int32_t tile_prefix[MAX_FRAMES + 1];
         __shared__ int32_t frame_start[MAX_FRAMES + 1];  // offsets[f0 + f]: first compact node of frame f
@@ -514,6 +532,7 @@ namespace tc {
         const uint32_t bar_empty     = smem_u32(&bars[STAGES]);
         const uint32_t bar_acc_full  = smem_u32(&bars[2 * STAGES]);
         const uint32_t bar_acc_empty = smem_u32(&bars[2 * STAGES + 2]);
+        const uint32_t bar_drain     = smem_u32(&bars[2 * STAGES + 4]);
 
         if (tid == 0) {
             failed_s = 0;
@@ -525,6 +544,7 @@ namespace tc {
                 mbar_init(bar_acc_full + 8 * i, 1);
                 mbar_init(bar_acc_empty + 8 * i, PRODUCER_WARPS);
             }
+            mbar_init(bar_drain, 1);
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
         for (int f = tid; f <= t.n_frames; f += CTA_THREADS) frame_start[f] = a.offsets[a.f0 + f];
@@ -568,14 +588,14 @@ namespace tc {
                 for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_count) {
                     const uint32_t ab  = tile_count & 1u;
                     const uint32_t acc = tmem_base + ab * (2 * NP);
-                    if (tile_count >= 2 && !mbar_wait_or_fail(bar_acc_empty + 8 * ab, ((tile_count >> 1) - 1) & 1u, failed)) {
+                    if (tile_count >= 2 && !mbar_wait_or_fail(bar_acc_empty + 8 * ab, ((tile_count >> 1) - 1) & 1u, failed, t.wait_limit)) {
                         ok = false;
                         break;
                     }
                     for (int u = 0; u < UNITS; ++u, ++it) {
                         const uint32_t stage = it % STAGES;
                         const uint32_t use   = it / STAGES;
-                        if (!mbar_wait_or_fail(bar_full + 8 * stage, use & 1u, failed)) {
+                        if (!mbar_wait_or_fail(bar_full + 8 * stage, use & 1u, failed, t.wait_limit)) {
                             ok = false;
                             break;
                         }
@@ -588,7 +608,16 @@ namespace tc {
                         if (u == UNITS - 1) commit(bar_acc_full + 8 * ab);
                     }
                 }
-                if (!ok) failed_s = 1;
+                if (!ok) {
+                    failed_s = 1;
+                    // Giving up: MMAs issued so far may still be running against this CTA's tensor memory and stages.
+                    // One more commit tracks them all; the tear-down below frees the tensor memory only after it (the
+                    // wait uses the full default limit whatever the kernel was told, and is itself bounded).
+                    if (it > 0) {
+                        commit(bar_drain);
+                        mbar_wait(bar_drain, 0u, WAIT_LIMIT);
+                    }
+                }
             }
         }
         else {
@@ -671,20 +700,27 @@ namespace tc {
                     const uint32_t it    = it0 + u;
                     const uint32_t stage = it % STAGES;
                     const uint32_t use   = it / STAGES;
-                    if (use > 0 && !mbar_wait_or_fail(bar_empty + 8 * stage, (use - 1) & 1u, failed)) ok = false;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint4(&b)[4]  = buf[(PH + u) % DEPTH];
-                    const uint32_t a_hi = a_base + lane_base + stage * 16;
-                    tmem_st8(a_hi, b[0], b[1]);
-                    tmem_st8(a_hi + 8, b[2], b[3]);
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    if (use > 0 && !mbar_wait_or_fail(bar_empty + 8 * stage, (use - 1) & 1u, failed, t.wait_limit)) {
+                        ok      = false;
+                        *failed = 1;
+                    }
+                    // the tensor-memory store is warp-collective, and a stage whose wait ran out may still be read by
+                    // the tensor core: the warp writes only while all of its lanes are good
+                    if (__all_sync(0xffffffffu, ok)) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint4(&b)[4]  = buf[(PH + u) % DEPTH];
+                        const uint32_t a_hi = a_base + lane_base + stage * 16;
+                        tmem_st8(a_hi, b[0], b[1]);
+                        tmem_st8(a_hi + 8, b[2], b[3]);
+                        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_full + 8 * stage);
                 }
                 ok = __all_sync(0xffffffffu, ok) && !*failed;
                 if (!ok) return false;
-                const bool arrived = mbar_wait_or_fail(bar_acc_full + 8 * ab, (tile_count >> 1) & 1u, failed);
+                const bool arrived = mbar_wait_or_fail(bar_acc_full + 8 * ab, (tile_count >> 1) & 1u, failed, t.wait_limit);
                 ok                 = __all_sync(0xffffffffu, arrived);
                 if (!ok) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");

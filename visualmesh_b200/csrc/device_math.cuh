@@ -65,14 +65,19 @@ __device__ __forceinline__ float as_host_libm(float approx, float x, const uint3
     ba += (d == 1u) ? 1u : (d == 3u) ? 0xFFFFFFFFu : 0u;
     return __uint_as_float(ba);
 }
+// Input ranges of the tables as float bit patterns, [first, end): 2^-27 up to 1 (acos) or 2 (sin, tan). The host side
+// builds the tables over the same ranges (libm_tables.hpp; the engine checks the two at compile time).
+constexpr uint32_t LIBM_FIRST_BITS = 0x32000000u;
+constexpr uint32_t LIBM_ONE_BITS   = 0x3F800000u;
+constexpr uint32_t LIBM_TWO_BITS   = 0x40000000u;
 __device__ __forceinline__ float acos_rn(float x, const uint32_t* table) {
-    return as_host_libm(__double2float_rn(acos(static_cast<double>(x))), x, table, 0x3A800000u, 0x3F800000u);
+    return as_host_libm(__double2float_rn(acos(static_cast<double>(x))), x, table, LIBM_FIRST_BITS, LIBM_ONE_BITS);
 }
 __device__ __forceinline__ float sin_rn(float x, const uint32_t* table) {
-    return as_host_libm(__double2float_rn(sin(static_cast<double>(x))), x, table, 0x3A800000u, 0x3F800000u);
+    return as_host_libm(__double2float_rn(sin(static_cast<double>(x))), x, table, LIBM_FIRST_BITS, LIBM_TWO_BITS);
 }
 __device__ __forceinline__ float tan_rn(float x, const uint32_t* table) {
-    return as_host_libm(__double2float_rn(tan(static_cast<double>(x))), x, table, 0x3A800000u, 0x40000000u);
+    return as_host_libm(__double2float_rn(tan(static_cast<double>(x))), x, table, LIBM_FIRST_BITS, LIBM_TWO_BITS);
 }
 
 // cpp/visualmesh/utility/projection.hpp:105-120: float products, double running sum, one rounding at the end

@@ -36,6 +36,9 @@ struct CudaFailure {
     cudaError_t code;
     const char* what;
 };
+// the per-frame constants could not be computed: a projection the lens math does not know (the reference throws from
+// unproject, cpp/visualmesh/utility/projection.hpp:224)
+struct UnsupportedLens {};
 
 #define VM_CUDA(expr)                                        \
     do {                                                     \
@@ -84,6 +87,11 @@ struct PinnedArray {
         cap = 0;
     }
 };
+
+static_assert(libm::FIRST_BITS[libm::ACOS] == LIBM_FIRST_BITS && libm::END_BITS[libm::ACOS] == LIBM_ONE_BITS
+                && libm::FIRST_BITS[libm::SIN] == LIBM_FIRST_BITS && libm::END_BITS[libm::SIN] == LIBM_TWO_BITS
+                && libm::FIRST_BITS[libm::TAN] == LIBM_FIRST_BITS && libm::END_BITS[libm::TAN] == LIBM_TWO_BITS,
+              "the device reads the last-bit tables over the ranges the host builds them for");
 
 // Device copies of the libm last-bit tables, built on first use and shared by all engines of a process (per device).
 constexpr int LIBM_MAX_DEVICES = 64;
@@ -150,6 +158,7 @@ struct StageTimer {
 }  // namespace vm
 
 struct vm_mesh {
+    const vm_engine* owner = nullptr;  // the engine it was uploaded through (and whose device holds it)
     int32_t n_nodes = 0, n_neighbours = 0, n_bsp = 0;
     float4* d_rays        = nullptr;
     int32_t* d_neighbours = nullptr;
@@ -193,7 +202,9 @@ struct vm_engine {
     int tc_mode      = 1;
     int tc_min_product = 512;   // mode 1: layers with C_in x C_out at least this run on the tensor cores
     bool tc_no_split = false;   // debugging: never use the split feature layout
+    uint32_t tc_wait_limit = 4000000;  // polls of one mbarrier wait in the tensor-core kernels (vm_set_wait_limit)
     cudaEvent_t ev_timer_start = nullptr, ev_timer_stop = nullptr;
+    cudaEvent_t ev_batch_start = nullptr;  // the start-of-batch clears (offsets[0], abort flag) are done
 };
 
 namespace vm {
@@ -318,7 +329,7 @@ static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, 
 }
 
 template <int CIN, int NP, int NSLOTS, bool HALF>
-static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
+static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, uint32_t wait_limit, cudaStream_t s) {
     constexpr int STAGES = CIN >= 32 ? 2 : 3;  // 32-channel stages are 16 KB: two of them leave room for a third CTA per SM
     const size_t smem    = tc::smem_bytes<CIN, NP, STAGES, HALF>(NSLOTS);
     static LaunchPlans plans;
@@ -342,13 +353,14 @@ static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frame
     t.n_frames   = n_frames;
     t.cout       = L.cout;
     t.abort_flag = abort_flag;
+    t.wait_limit = wait_limit;
     const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
     const int grid        = std::max(1, std::min(tiles_upper, plan.n_sms * plan.ctas_per_sm));
     tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
 }
 
 template <int CIN, int NP, int NSLOTS>
-static void launch_conv_tc_tmem_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, cudaStream_t s) {
+static void launch_conv_tc_tmem_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, uint32_t wait_limit, cudaStream_t s) {
     const size_t smem = tc::smem_bytes_tmem<CIN, NP>(NSLOTS);
     static LaunchPlans plans;
     const LaunchPlan& plan = plans.get([smem](int dev) {
@@ -374,6 +386,7 @@ static void launch_conv_tc_tmem_t(const DenseLayer& L, const ConvArgs& a, int n_
     t.n_frames   = n_frames;
     t.cout       = L.cout;
     t.abort_flag = abort_flag;
+    t.wait_limit = wait_limit;
     const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
     const int grid        = std::max(1, std::min(tiles_upper, plan.n_sms * plan.ctas_per_sm));
     tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
@@ -387,7 +400,7 @@ static bool has_tc_split_kernel(const DenseLayer& L) {
 static bool launch_conv_tc_split(vm_engine* e, const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, cudaStream_t s) {
 #define VM_TCS(CI, NPAD, NS)                                                              \
     if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS) {                               \
-        launch_conv_tc_tmem_t<CI, NPAD, NS>(L, a, n_frames, max_rows, e->d_abort, s);       \
+        launch_conv_tc_tmem_t<CI, NPAD, NS>(L, a, n_frames, max_rows, e->d_abort, e->tc_wait_limit, s);       \
         return true;                                                                       \
     }
     VM_TCS(16, 16, 5) VM_TCS(16, 16, 7) VM_TCS(16, 16, 9) VM_TCS(16, 32, 5) VM_TCS(16, 32, 7) VM_TCS(16, 32, 9)
@@ -400,7 +413,7 @@ static bool launch_conv_tc(vm_engine* e, const DenseLayer& L, const ConvArgs& a,
     if (L.tc_np == 0 || n_frames > tc::MAX_FRAMES) return false;
 #define VM_TC(CI, NPAD, NS, HF)                                                      \
     if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS && L.tc_half == HF) {        \
-        launch_conv_tc_t<CI, NPAD, NS, HF>(L, a, n_frames, max_rows, e->d_abort, s);   \
+        launch_conv_tc_t<CI, NPAD, NS, HF>(L, a, n_frames, max_rows, e->d_abort, e->tc_wait_limit, s);   \
         return true;                                                                  \
     }
     VM_TC(8, 16, 5, false) VM_TC(8, 16, 7, false) VM_TC(8, 16, 9, false)
@@ -413,6 +426,24 @@ static bool launch_conv_tc(vm_engine* e, const DenseLayer& L, const ConvArgs& a,
 }
 
 enum ConvKind { CONV_FFMA = 0, CONV_TC_GATHER = 1, CONV_TC_SPLIT = 2 };
+
+// The tensor-core kernel that gathers fp32 rows itself exists for these shapes (the VM_TC list of launch_conv_tc).
+static bool has_tc_gather_kernel(const DenseLayer& L) {
+    if (L.tc_np == 0) return false;
+    const int ns = L.n_slots;
+    if (!L.tc_half) return L.cin == 8 && L.tc_np == 16 && (ns == 5 || ns == 7 || ns == 9);
+    if (L.cin == 16 && L.tc_np == 16) return ns == 5 || ns == 7 || ns == 9;
+    if ((L.cin == 16 && L.tc_np == 32) || (L.cin == 32 && (L.tc_np == 16 || L.tc_np == 32))) return ns == 7 || ns == 9;
+    return false;
+}
+
+// Whether the kernel that runs layer L as `kind` honours ConvArgs::out_split. The tensor-core kernels write the split
+// layout when their tile is exactly as wide as the layer; the specialised FFMA kernels when the width is a multiple
+// of 8; the generic kernel never does.
+static bool producer_writes_split(const DenseLayer& L, ConvKind kind) {
+    if (kind != CONV_FFMA) return L.cout == L.tc_np;
+    return has_fast_ffma_kernel(L.cin, L.cout) && L.cout % 8 == 0;
+}
 
 static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_frames, int max_rows, cudaStream_t s, ConvKind kind) {
     a.weights     = L.d_weights;
@@ -452,10 +483,10 @@ static void run_network(vm_engine* e,
         const DenseLayer& L = e->layers[l];
         if (!e->use_tc || L.tc_np == 0 || n_frames > tc::MAX_FRAMES) continue;
         if (e->tc_mode == 1 && L.cin * L.cout < e->tc_min_product) continue;
-        const bool producer_can_split =
-          l > 0 && L.n_slots > 1 && (kind[l - 1] != CONV_FFMA || has_fast_ffma_kernel(e->layers[l - 1].cin, e->layers[l - 1].cout));
-        kind[l] = (has_tc_split_kernel(L) && producer_can_split && !e->tc_no_split) ? CONV_TC_SPLIT : CONV_TC_GATHER;
-        if (kind[l] == CONV_TC_GATHER && L.n_slots == 1) kind[l] = CONV_FFMA;  // dense-only layers have no tensor-core kernel
+        const bool producer_can_split = l > 0 && L.n_slots > 1 && producer_writes_split(e->layers[l - 1], kind[l - 1]);
+        if (has_tc_split_kernel(L) && producer_can_split && !e->tc_no_split) kind[l] = CONV_TC_SPLIT;
+        else if (L.n_slots > 1 && has_tc_gather_kernel(L)) kind[l] = CONV_TC_GATHER;
+        // anything else (dense-only layers, shapes without a tensor-core instantiation) stays on the FFMA kernels
     }
     int cur = 0;
     for (size_t l = 0; l < n_layers; ++l) {
@@ -559,7 +590,7 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
         const vm_frame& fr = frames[f];
         FrameParams& p     = lane.h_frames.p[f - f0];
         std::memset(&p, 0, sizeof(p));
-        fill_frame_params(fr, p, e->device);
+        if (!fill_frame_params(fr, p, e->device)) throw UnsupportedLens{};
         const int64_t nc = frame_candidates(fr);
         p.n_candidates   = static_cast<int32_t>(nc);
         p.cand_off       = static_cast<int32_t>(cand_total);
@@ -734,6 +765,7 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
     for (int f = 0; f < n_frames; ++f) {
         const vm_frame& fr = frames[f];
         if (fr.mesh == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "frame without a mesh");
+        if (fr.mesh->owner != e) return fail(VM_ERR_INVALID_ARGUMENT, "mesh was uploaded through another engine");
         if (fr.mesh->n_neighbours != N) return fail(VM_ERR_INVALID_ARGUMENT, "frames of one batch must share n_neighbours");
         if (fr.lens.projection != VM_RECTILINEAR && fr.lens.projection != VM_EQUISOLID && fr.lens.projection != VM_EQUIDISTANT) {
             return fail(VM_ERR_UNSUPPORTED_LENS, "Cannot project: Unknown lens type");
@@ -784,6 +816,9 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
         *e->h_abort       = 0;
         VM_CUDA(cudaMemsetAsync(e->d_offsets.p, 0, sizeof(int32_t), e->lanes[0].stream));
         VM_CUDA(cudaMemsetAsync(e->d_abort, 0, sizeof(int32_t), e->lanes[0].stream));
+        // kernels of the other lanes raise the same abort flag: their first chunk must not start before the clear
+        VM_CUDA(cudaEventRecord(e->ev_batch_start, e->lanes[0].stream));
+        for (int l = 1; l < n_lanes; ++l) VM_CUDA(cudaStreamWaitEvent(e->lanes[l].stream, e->ev_batch_start, 0));
 
         // chunks: runs of frames bounded by a candidate budget and a frame count. Small chunks let the copies of one
         // chunk overlap the kernels of another; when there is nothing to copy in (frames already on the device, or
@@ -823,7 +858,13 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
             ++chunk;
         }
         if (prev != nullptr) enqueue_chunk_readback(e, *prev, N, classify, to_host);
-        VM_CUDA(cudaMemcpyAsync(e->h_abort, e->d_abort, sizeof(int32_t), cudaMemcpyDeviceToHost, e->lanes[(chunk - 1) % n_lanes].stream));
+        // the abort flag is read once, after the last kernel of EVERY lane: the chunks before the last one run on
+        // other streams and may still be in their network layers when the last chunk's stream gets here
+        cudaStream_t last_stream = e->lanes[(chunk - 1) % n_lanes].stream;
+        for (int l = 0; l < n_lanes; ++l) {
+            if (e->lanes[l].busy && e->lanes[l].stream != last_stream) VM_CUDA(cudaStreamWaitEvent(last_stream, e->lanes[l].ev_done, 0));
+        }
+        VM_CUDA(cudaMemcpyAsync(e->h_abort, e->d_abort, sizeof(int32_t), cudaMemcpyDeviceToHost, last_stream));
         for (int l = 0; l < n_lanes; ++l) {
             VM_CUDA(cudaStreamSynchronize(e->lanes[l].stream));
             e->lanes[l].busy = false;
@@ -868,6 +909,14 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
         cudaGetLastError();
         const vm_status s = f.code == cudaErrorMemoryAllocation ? VM_ERR_OUT_OF_MEMORY : VM_ERR_CUDA;
         return fail(s, std::string(cudaGetErrorName(f.code)) + ": " + cudaGetErrorString(f.code) + " in " + f.what);
+    }
+    catch (const UnsupportedLens&) {
+        // work already enqueued for earlier chunks finishes on its own; the lanes are drained before the next batch
+        for (int l = 0; l < MAX_LANES; ++l) {
+            cudaStreamSynchronize(e->lanes[l].stream);
+            e->lanes[l].busy = false;
+        }
+        return fail(VM_ERR_UNSUPPORTED_LENS, "Cannot project: Unknown lens type");
     }
 }
 
@@ -951,6 +1000,7 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
         }
         VM_CUDA(cudaEventCreate(&e->ev_timer_start));
         VM_CUDA(cudaEventCreate(&e->ev_timer_stop));
+        VM_CUDA(cudaEventCreateWithFlags(&e->ev_batch_start, cudaEventDisableTiming));
         VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&e->d_abort), sizeof(int32_t)));
         VM_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&e->h_abort), sizeof(int32_t), cudaHostAllocDefault));
         int l = 0;
@@ -1085,6 +1135,7 @@ void vm_engine_destroy(vm_engine* e) {
     for (auto ev : e->event_pool) cudaEventDestroy(ev);
     if (e->ev_timer_start) cudaEventDestroy(e->ev_timer_start);
     if (e->ev_timer_stop) cudaEventDestroy(e->ev_timer_stop);
+    if (e->ev_batch_start) cudaEventDestroy(e->ev_batch_start);
     cudaFree(e->d_abort);
     cudaFreeHost(e->h_abort);
     delete e;
@@ -1099,6 +1150,7 @@ vm_status vm_mesh_upload(vm_engine* e, const float* rays, const int32_t* neighbo
     std::unique_ptr<vm_mesh> m(new vm_mesh());
     try {
         VM_CUDA(cudaSetDevice(e->device));
+        m->owner        = e;
         m->n_nodes      = n_nodes;
         m->n_neighbours = n_neighbours;
         // rays padded to float4 as the OpenCL engine does (cpp/visualmesh/engine/opencl/engine.hpp:611-615)
@@ -1203,6 +1255,15 @@ vm_status vm_sample(vm_engine* e, const float* px, int32_t n, const void* image,
     const int cls = format_class(format);
     if (cls == FMT_UNKNOWN) return fail(VM_ERR_UNSUPPORTED_FORMAT, "Unsupported image format");
     if (n == 0) return VM_OK;
+    // The reference reads whatever address a coordinate outside the image leads to (cpp/visualmesh/engine/cpu/
+    // pixel.hpp:131-134 clamp only one side); the engine itself only samples points that passed the on-screen test.
+    // Here the coordinates come from the caller, so they are checked: a read outside the image would be a GPU fault.
+    for (int32_t i = 0; i < n; ++i) {
+        const float x = px[2 * i], y = px[2 * i + 1];
+        if (!(x >= 0.0f && x <= static_cast<float>(width - 1) && y >= 0.0f && y <= static_cast<float>(height - 1))) {
+            return fail(VM_ERR_INVALID_ARGUMENT, "pixel coordinate " + std::to_string(i) + " is outside the image (or not finite)");
+        }
+    }
     try {
         VM_CUDA(cudaSetDevice(e->device));
         Lane& lane        = e->lanes[0];
@@ -1291,6 +1352,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[ST_BYTES];
 
 constexpr int ST_MAX_DEVICES = 64;
 unsigned char* g_static_address[ST_MAX_DEVICES] = {};
+std::once_flag g_static_once[ST_MAX_DEVICES];
 }  // namespace
 
 vm_status vm_project_static(vm_engine* e,
@@ -1308,6 +1370,8 @@ vm_status vm_project_static(vm_engine* e,
     if (lens->projection != VM_RECTILINEAR && lens->projection != VM_EQUISOLID && lens->projection != VM_EQUIDISTANT) {
         return fail(VM_ERR_UNSUPPORTED_LENS, "Cannot project: Unknown lens type");
     }
+    if (lens->dimensions[0] <= 0 || lens->dimensions[1] <= 0) return fail(VM_ERR_INVALID_ARGUMENT, "lens dimensions must be positive");
+    if (mesh->owner != e) return fail(VM_ERR_INVALID_ARGUMENT, "mesh was uploaded through another engine");
     if (mesh->n_bsp == 0) return fail(VM_ERR_NO_BSP, "vm_project_static looks up on the device: the mesh needs vm_mesh_set_bsp");
     if (mesh->n_nodes > VM_STATIC_MAX_NODES) {
         return fail(VM_ERR_INVALID_ARGUMENT, "mesh has " + std::to_string(mesh->n_nodes) + " nodes; vm_project_static holds at most VM_STATIC_MAX_NODES = "
@@ -1320,13 +1384,16 @@ vm_status vm_project_static(vm_engine* e,
     if (e->device < 0 || e->device >= ST_MAX_DEVICES) return fail(VM_ERR_INVALID_ARGUMENT, "device ordinal out of range");
     try {
         VM_CUDA(cudaSetDevice(e->device));
-        if (g_static_address[e->device] == nullptr) {
-            // once per device, with that device current
+        // once per device, with that device current; engines of several host threads may get here together
+        cudaError_t lookup = cudaSuccess;
+        std::call_once(g_static_once[e->device], [&] {
             unsigned char* address = nullptr;
-            VM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch));
-            g_static_address[e->device] = address;
-        }
-        unsigned char* base   = g_static_address[e->device];
+            lookup = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch);
+            if (lookup == cudaSuccess) g_static_address[e->device] = address;
+        });
+        if (lookup != cudaSuccess) throw CudaFailure{lookup, "cudaGetSymbolAddress(g_static_scratch)"};
+        unsigned char* base = g_static_address[e->device];
+        if (base == nullptr) return fail(VM_ERR_CUDA, "the address of the static scratch array could not be looked up on this device");
         auto* d_frame         = reinterpret_cast<FrameParams*>(base + ST_FRAME);
         auto* d_cells         = reinterpret_cast<int32_t*>(base + ST_CELLS);  // [0], [1] offsets, [2] abort
         auto* d_blocks        = reinterpret_cast<int32_t*>(base + ST_BLOCKS);
@@ -1416,6 +1483,12 @@ vm_status vm_timer_stop(vm_engine* e, float* milliseconds) {
         cudaGetLastError();
         return fail(VM_ERR_CUDA, std::string(cudaGetErrorName(f.code)) + " in " + f.what);
     }
+    return VM_OK;
+}
+
+vm_status vm_set_wait_limit(vm_engine* e, uint32_t polls) {
+    if (e == nullptr) return fail(VM_ERR_INVALID_ARGUMENT, "null engine");
+    e->tc_wait_limit = polls;
     return VM_OK;
 }
 

@@ -5,11 +5,16 @@
 // the same functions in double precision and rounds once, which lands within one ulp of whatever the host libm
 // returns. To return exactly what the host libm returns - on this machine, whichever libm version it runs - the
 // engine tabulates, once per process and function, the low two bits of libm's result for every float in the input
-// range that matters (2 bits per input, 21-23 MB per function). The device then picks, among its own result and its
-// two neighbouring floats, the one whose low two bits match: three consecutive bit patterns have distinct residues
-// modulo four, so the choice is unique whenever the two sides are within one ulp.
-// Inputs outside the tabulated range (rays within 0.06 degrees of the plane perpendicular to the optical axis or
-// behind it) keep the device's correctly rounded value.
+// range that can occur for an on-screen node (2 bits per input, 57-59 MB per function). The device then picks, among
+// its own result and its two neighbouring floats, the one whose low two bits match: three consecutive bit patterns have
+// distinct residues modulo four, so the choice is unique whenever the two sides are within one ulp.
+// The tables start at 2^-27. Below that, sin(t) = tan(t) = t and acos(x) = float(pi / 2) in single precision for any
+// libm that is within one ulp (glibc 2.39 was checked over every float below 2^-24: its only results that differ from
+// the correctly rounded ones are acosf at five inputs near 1.59e-8, which the table covers). Inputs outside the tables
+// keep the device's correctly rounded value: x <= 0 for acos (a ray in or behind the plane perpendicular to the optical
+// axis, on screen only for a lens whose field of view exceeds 180 degrees) and theta / 2 >= 2 for sin (never: theta
+// is at most pi). There the pixel coordinate can differ from the reference's by one ulp of theta (2.4e-7 rad, under
+// 3e-4 px for the focal lengths of a megapixel camera), inside the 1e-3 px tolerance.
 #pragma once
 
 #include <cmath>
@@ -24,12 +29,15 @@ namespace libm {
     enum Function { ACOS = 0, SIN = 1, TAN = 2, N_FUNCTIONS = 3 };
 
     // [first, first + count) in float bit patterns: positive floats only, whole binades
+    constexpr uint32_t TABLE_FIRST     = 0x32000000u;  // 2^-27
+    constexpr uint32_t TABLE_END_ONE   = 0x3F800000u;  // 1
+    constexpr uint32_t TABLE_END_TWO   = 0x40000000u;  // 2
     constexpr uint32_t FIRST_BITS[N_FUNCTIONS] = {
-      0x3A800000u,  // acos: x in [2^-10, 1)
-      0x3A800000u,  // sin:  t in [2^-10, 1)   (t = theta / 2)
-      0x3A800000u,  // tan:  t in [2^-10, 2)   (t = theta clamped to [0, pi/2])
+      TABLE_FIRST,  // acos: x in [2^-27, 1)
+      TABLE_FIRST,  // sin:  t in [2^-27, 2)   (t = theta / 2 <= pi / 2)
+      TABLE_FIRST,  // tan:  t in [2^-27, 2)   (t = theta clamped to [0, pi/2])
     };
-    constexpr uint32_t END_BITS[N_FUNCTIONS] = {0x3F800000u, 0x3F800000u, 0x40000000u};
+    constexpr uint32_t END_BITS[N_FUNCTIONS] = {TABLE_END_ONE, TABLE_END_TWO, TABLE_END_TWO};
 
     inline uint32_t count(int fn) {
         return END_BITS[fn] - FIRST_BITS[fn];

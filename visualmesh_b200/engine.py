@@ -354,6 +354,11 @@ class Engine:
         abi.check(self._lib.vm_timer_stop(self._ptr, C.byref(ms)))
         return float(ms.value)
 
+    def set_wait_limit(self, polls: int) -> None:
+        """Polls one bounded wait of the tensor-core kernels makes before the kernel gives up and the call fails with
+        VM_ERR_DEVICE_ABORT (vm_set_wait_limit); 0 makes every such wait give up at once."""
+        abi.check(self._lib.vm_set_wait_limit(self._ptr, int(polls)))
+
     def launch_count(self) -> int:
         return int(self._lib.vm_launch_count(self._ptr))
 
