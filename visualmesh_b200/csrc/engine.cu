@@ -20,7 +20,7 @@
 #include "../../include/vmcuda.h"
 #include "host_math.hpp"
 #include "kernels.cuh"
-#include "conv_tc.cuh"
+#include "conv_dispatch.hpp"
 #include "libm_tables.hpp"
 
 namespace vm {
@@ -32,19 +32,9 @@ static vm_status fail(vm_status s, const std::string& msg) {
     return s;
 }
 
-struct CudaFailure {
-    cudaError_t code;
-    const char* what;
-};
 // the per-frame constants could not be computed: a projection the lens math does not know (the reference throws from
 // unproject, cpp/visualmesh/utility/projection.hpp:224)
 struct UnsupportedLens {};
-
-#define VM_CUDA(expr)                                        \
-    do {                                                     \
-        cudaError_t vm_e_ = (expr);                          \
-        if (vm_e_ != cudaSuccess) throw CudaFailure{vm_e_, #expr}; \
-    } while (0)
 
 // Grow-only device and pinned-host arrays (the reference's OpenCL engine keeps the same kind of caches,
 // cpp/visualmesh/engine/opencl/engine.hpp:740-835).
@@ -115,18 +105,6 @@ static const uint32_t* libm_table(int device, int fn, bool build_if_missing) {
     return g_libm_device[device][fn];
 }
 
-struct DenseLayer {
-    float* d_weights = nullptr;  // [n_slots * cin][coutp] then [coutp] biases
-    int cin = 0, cout = 0, coutp = 0, n_slots = 1, activation = 0;
-    std::string stage;  // name under which this layer's kernel is timed, e.g. "graph_conv_16x16"
-    std::vector<float> host_packed;  // [K][coutp] weights then biases, as on the device (for parameter-space kernels)
-    // tensor-core path (conv_tc.cuh): weights split into TF32 hi/lo parts in the UMMA K-major layout, padded bias
-    void* d_tc_cat   = nullptr;  // [K / KCH chunks][2 * NP rows][16 B]: hi rows then lo rows
-    float* d_tc_bias = nullptr;
-    int tc_np        = 0;      // padded output width of the tensor-core tile, 0 = no tensor-core path for this shape
-    bool tc_half     = false;  // fp16 hi/lo split (16- and 32-channel inputs) or TF32 split (8-channel inputs)
-};
-
 constexpr int MAX_LANES = 3;
 
 struct Lane {
@@ -148,6 +126,11 @@ struct Lane {
     DeviceArray<int32_t> d_node_rank;
     DeviceArray<float> d_feat[2];
     DeviceArray<uint8_t> d_images;
+    // tile plan of the chunk for the staged tensor-core layers (conv_staged.cuh)
+    DeviceArray<uint16_t> d_nbl;
+    DeviceArray<int32_t> d_halo_rows;
+    DeviceArray<int32_t> d_halo_count;
+    bool plan_valid = false;
 };
 
 struct StageTimer {
@@ -202,9 +185,13 @@ struct vm_engine {
     int tc_mode      = 1;
     int tc_min_product = 512;   // mode 1: layers with C_in x C_out at least this run on the tensor cores
     bool tc_no_split = false;   // debugging: never use the split feature layout
-    uint32_t tc_wait_limit = 4000000;  // polls of one mbarrier wait in the tensor-core kernels (vm_set_wait_limit)
+    bool staged          = true;    // tensor-core layers read their gather from shared-memory windows (conv_staged.cuh)
+    bool may_stage       = false;   // some layer could run as a staged tensor-core layer under the engine's policy
+    uint32_t tc_wait_limit = vm::TC_DEFAULT_WAIT_LIMIT;  // polls of one mbarrier wait in the tensor-core kernels (vm_set_wait_limit)
     cudaEvent_t ev_timer_start = nullptr, ev_timer_stop = nullptr;
     cudaEvent_t ev_batch_start = nullptr;  // the start-of-batch clears (offsets[0], abort flag) are done
+    cudaEvent_t ev_batch_done  = nullptr;  // everything of the batch, the abort flag's copy included, has finished
+    bool blocking_sync         = false;    // host waits sleep instead of spinning
 };
 
 namespace vm {
@@ -227,236 +214,36 @@ static void end_stage(vm_engine* e, cudaStream_t s) {
     VM_CUDA(cudaEventRecord(e->timers.back().stop, s));
 }
 
-// ---- graph convolution dispatch ----------------------------------------------------------------------------------
-
-// layer shapes (C_in, C_out, rows per thread) with a specialised FFMA kernel
-#define VM_CONV_SHAPES(X)                                                                                   \
-    X(4, 2, 4) X(4, 3, 4) X(4, 4, 4) X(4, 8, 4) X(4, 12, 4) X(4, 16, 4) X(4, 32, 2)                         \
-    X(8, 2, 4) X(8, 3, 4) X(8, 4, 4) X(8, 5, 4) X(8, 8, 4) X(8, 12, 4) X(8, 16, 4)                          \
-    X(12, 2, 4) X(12, 3, 4) X(12, 4, 4) X(12, 8, 4) X(12, 12, 4) X(12, 16, 4)                               \
-    X(16, 2, 4) X(16, 3, 4) X(16, 4, 4) X(16, 5, 4) X(16, 8, 4) X(16, 12, 4) X(16, 16, 4) X(16, 32, 2)      \
-    X(32, 2, 4) X(32, 3, 4) X(32, 4, 4) X(32, 8, 4) X(32, 16, 4) X(32, 32, 2)
-
-static bool has_fast_ffma_kernel(int cin, int cout) {
-#define VM_IS(CI, CO, RR) if (cin == CI && cout == CO) return true;
-    VM_CONV_SHAPES(VM_IS)
-#undef VM_IS
-    return false;
-}
-
-// What a launcher works out once per kernel instantiation and device: function attributes are per device, and engine
-// instances of several host threads may reach a launcher at the same time.
-struct LaunchPlan {
-    int ctas_per_sm = 0;
-    int n_sms       = 0;
-};
-constexpr int MAX_DEVICES = 64;
-struct LaunchPlans {
-    LaunchPlan plan[MAX_DEVICES];
-    std::once_flag once[MAX_DEVICES];
-    template <typename Init>
-    const LaunchPlan& get(Init init) {
-        int dev = 0;
-        VM_CUDA(cudaGetDevice(&dev));
-        dev = std::min(std::max(dev, 0), MAX_DEVICES - 1);
-        std::call_once(once[dev], [&] { plan[dev] = init(dev); });
-        return plan[dev];
-    }
-};
-
-template <int CIN, int COUT, int R, int T = CONV_THREADS, int MINB = 1>
-static void launch_conv_t(const ConvArgs& a, dim3 grid_rows, int max_rows, cudaStream_t s) {
-    constexpr int COUTP = (COUT + 3) & ~3;
-    const size_t smem   = (static_cast<size_t>(a.n_slots) * CIN * COUTP + COUTP) * sizeof(float);
-    static LaunchPlans plans;
-    plans.get([](int) {
-        VM_CUDA(cudaFuncSetAttribute(k_graph_conv<CIN, COUT, R, T, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-        return LaunchPlan{};
-    });
-    dim3 grid((max_rows + T * R - 1) / (T * R), grid_rows.y);
-    k_graph_conv<CIN, COUT, R, T, MINB><<<grid, T, smem, s>>>(a);
-}
-
-constexpr int CW_MAX = 2320;  // floats: a 16 -> 16 layer with 8 neighbours and its biases
-
-template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS>
-static bool launch_conv_cw(const DenseLayer& L, const ConvArgs& a, dim3 grid_rows, int max_rows, cudaStream_t s) {
-    if (L.host_packed.size() > static_cast<size_t>(WMAX)) return false;
-    ConvWeights<WMAX> wp;
-    std::memcpy(wp.w, L.host_packed.data(), L.host_packed.size() * sizeof(float));
-    dim3 grid((max_rows + T * R - 1) / (T * R), grid_rows.y);
-    // Layers bound by the latency of their gather rather than by the FP32 pipe - 4-channel first layers, 8 -> 8, and
-    // the narrow last layers - run with the slot loop unrolled (slot count as a template parameter): the loads of the
-    // next slots are then issued ahead of the current slot's arithmetic. Measured on 4.4 M rows: 4 -> 16 183 -> 114 us
-    // (with the weights in the parameter space instead of shared memory), 8 -> 8 133 -> 112 us, 32 -> 4 448 -> 413 us;
-    // the 16- and 32-channel layers in between, bound by the FP32 pipe, measured 3-6 % slower unrolled and stay rolled.
-    constexpr bool LATENCY_BOUND = (CIN == 8 && COUT == 8) || CIN == 4 || COUT <= 4;
-    if (LATENCY_BOUND && a.n_slots == 5) { k_graph_conv_cw<CIN, COUT, R, WMAX, T, LATENCY_BOUND ? 5 : 0><<<grid, T, 0, s>>>(a, wp); }
-    else if (LATENCY_BOUND && a.n_slots == 7) {
-        k_graph_conv_cw<CIN, COUT, R, WMAX, T, LATENCY_BOUND ? 7 : 0><<<grid, T, 0, s>>>(a, wp);
-    }
-    else if (LATENCY_BOUND && a.n_slots == 9) {
-        k_graph_conv_cw<CIN, COUT, R, WMAX, T, LATENCY_BOUND ? 9 : 0><<<grid, T, 0, s>>>(a, wp);
-    }
-    else {
-        k_graph_conv_cw<CIN, COUT, R, WMAX, T><<<grid, T, 0, s>>>(a, wp);
-    }
-    return true;
-}
-
-// Shapes with a specialised kernel; anything else takes the generic one.
-static bool launch_conv_fast(const DenseLayer& L, const ConvArgs& a, dim3 grid, int max_rows, cudaStream_t s) {
-    const size_t smem = (static_cast<size_t>(a.n_slots) * L.cin * L.coutp + L.coutp) * sizeof(float);
-    if (smem > 96 * 1024) return false;
-    // weights small enough for the kernel parameter space are read through the constant cache (measured 15-40 %
-    // faster than the shared-memory copy: the weight reads leave the L1/shared data path to the gather)
-    static const bool const_weights = [] {
-        const char* v = std::getenv("VMCUDA_CONST_WEIGHTS");
-        return v == nullptr || v[0] != '0';
-    }();
-    // the 16 -> 16 layer measured best with two rows per thread and 256 threads
-    if (const_weights && L.cin == 16 && L.cout == 16 && launch_conv_cw<16, 16, 2, CW_MAX, 256>(L, a, grid, max_rows, s)) return true;
-#define VM_CONV(CI, CO, RR)                                                                       \
-    if (L.cin == CI && L.cout == CO) {                                                            \
-        /* parameter-space weights: two rows per thread and 256 threads measured best for every shape tried */ \
-        if (const_weights && launch_conv_cw<CI, CO, 2, CW_MAX, 256>(L, a, grid, max_rows, s)) return true; \
-        launch_conv_t<CI, CO, RR>(a, grid, max_rows, s);                                          \
-        return true;                                                                              \
-    }
-    VM_CONV_SHAPES(VM_CONV)
-#undef VM_CONV
-    return false;
-}
-
-template <int CIN, int NP, int NSLOTS, bool HALF>
-static void launch_conv_tc_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, uint32_t wait_limit, cudaStream_t s) {
-    constexpr int STAGES = CIN >= 32 ? 2 : 3;  // 32-channel stages are 16 KB: two of them leave room for a third CTA per SM
-    const size_t smem    = tc::smem_bytes<CIN, NP, STAGES, HALF>(NSLOTS);
-    static LaunchPlans plans;
-    const LaunchPlan& plan = plans.get([smem](int dev) {
-        LaunchPlan p;
-        VM_CUDA(cudaFuncSetAttribute(tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        VM_CUDA(cudaDeviceGetAttribute(&p.n_sms, cudaDevAttrMultiProcessorCount, dev));
-        // resident CTAs per SM: shared memory (about 220 KB usable, some per CTA reserved) and tensor memory (512 columns)
-        const int by_smem = static_cast<int>((220 * 1024) / (smem + 2048));
-        const int by_tmem = 512 / (4 * NP);
-        cudaFuncAttributes attr;
-        VM_CUDA(cudaFuncGetAttributes(&attr, tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF>));
-        const int regs_per_warp = (((attr.numRegs + 7) / 8 * 8) * 32 + 511) / 512 * 512;
-        const int by_regs       = 65536 / std::max(1, regs_per_warp * (tc::CTA_THREADS / 32));
-        p.ctas_per_sm           = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
-        return p;
-    });
-    tc::Args t{};
-    t.w_cat      = L.d_tc_cat;
-    t.bias       = L.d_tc_bias;
-    t.n_frames   = n_frames;
-    t.cout       = L.cout;
-    t.abort_flag = abort_flag;
-    t.wait_limit = wait_limit;
-    const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
-    const int grid        = std::max(1, std::min(tiles_upper, plan.n_sms * plan.ctas_per_sm));
-    tc::k_graph_conv_tc<CIN, NP, STAGES, NSLOTS, HALF><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
-}
-
-template <int CIN, int NP, int NSLOTS>
-static void launch_conv_tc_tmem_t(const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, int32_t* abort_flag, uint32_t wait_limit, cudaStream_t s) {
-    const size_t smem = tc::smem_bytes_tmem<CIN, NP>(NSLOTS);
-    static LaunchPlans plans;
-    const LaunchPlan& plan = plans.get([smem](int dev) {
-        LaunchPlan p;
-        if (smem > 48 * 1024) {
-            VM_CUDA(cudaFuncSetAttribute(tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        }
-        VM_CUDA(cudaDeviceGetAttribute(&p.n_sms, cudaDevAttrMultiProcessorCount, dev));
-        const int by_smem = static_cast<int>((220 * 1024) / (smem + 2048));
-        const int by_tmem = 512 / tc::tmem_columns<NP>();
-        cudaFuncAttributes attr;
-        VM_CUDA(cudaFuncGetAttributes(&attr, tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS>));
-        // registers: 8 per thread at a time, 512 per warp at a time, 64 K per SM
-        const int regs_per_warp = (((attr.numRegs + 7) / 8 * 8) * 32 + 511) / 512 * 512;
-        const int by_regs       = 65536 / std::max(1, regs_per_warp * (tc::CTA_THREADS / 32));
-        p.ctas_per_sm           = std::max(1, std::min(std::min(by_smem, by_tmem), std::min(by_regs, 8)));
-        if (const char* v = std::getenv("VMCUDA_TC_CTAS")) p.ctas_per_sm = std::max(1, std::min(p.ctas_per_sm, std::atoi(v)));
-        return p;
-    });
-    tc::Args t{};
-    t.w_cat      = L.d_tc_cat;
-    t.bias       = L.d_tc_bias;
-    t.n_frames   = n_frames;
-    t.cout       = L.cout;
-    t.abort_flag = abort_flag;
-    t.wait_limit = wait_limit;
-    const int tiles_upper = n_frames * ((max_rows + tc::TILE_ROWS - 1) / tc::TILE_ROWS);
-    const int grid        = std::max(1, std::min(tiles_upper, plan.n_sms * plan.ctas_per_sm));
-    tc::k_graph_conv_tc_tmem<CIN, NP, NSLOTS><<<grid, tc::CTA_THREADS, smem, s>>>(a, t);
-}
-
-// The tensor-core kernel fed from the split feature layout exists for these shapes.
-static bool has_tc_split_kernel(const DenseLayer& L) {
-    return L.tc_np != 0 && L.tc_half && (L.cin == 16 || L.cin == 32) && (L.n_slots == 5 || L.n_slots == 7 || L.n_slots == 9);
-}
-
-static bool launch_conv_tc_split(vm_engine* e, const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, cudaStream_t s) {
-#define VM_TCS(CI, NPAD, NS)                                                              \
-    if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS) {                               \
-        launch_conv_tc_tmem_t<CI, NPAD, NS>(L, a, n_frames, max_rows, e->d_abort, e->tc_wait_limit, s);       \
-        return true;                                                                       \
-    }
-    VM_TCS(16, 16, 5) VM_TCS(16, 16, 7) VM_TCS(16, 16, 9) VM_TCS(16, 32, 5) VM_TCS(16, 32, 7) VM_TCS(16, 32, 9)
-    VM_TCS(32, 16, 5) VM_TCS(32, 16, 7) VM_TCS(32, 16, 9) VM_TCS(32, 32, 5) VM_TCS(32, 32, 7) VM_TCS(32, 32, 9)
-#undef VM_TCS
-    return false;
-}
-
-static bool launch_conv_tc(vm_engine* e, const DenseLayer& L, const ConvArgs& a, int n_frames, int max_rows, cudaStream_t s) {
-    if (L.tc_np == 0 || n_frames > tc::MAX_FRAMES) return false;
-#define VM_TC(CI, NPAD, NS, HF)                                                      \
-    if (L.cin == CI && L.tc_np == NPAD && L.n_slots == NS && L.tc_half == HF) {        \
-        launch_conv_tc_t<CI, NPAD, NS, HF>(L, a, n_frames, max_rows, e->d_abort, e->tc_wait_limit, s);   \
-        return true;                                                                  \
-    }
-    VM_TC(8, 16, 5, false) VM_TC(8, 16, 7, false) VM_TC(8, 16, 9, false)
-    VM_TC(16, 16, 5, true) VM_TC(16, 16, 7, true) VM_TC(16, 16, 9, true)
-    VM_TC(16, 32, 7, true) VM_TC(16, 32, 9, true)
-    VM_TC(32, 16, 7, true) VM_TC(32, 16, 9, true)
-    VM_TC(32, 32, 7, true) VM_TC(32, 32, 9, true)
-#undef VM_TC
-    return false;
-}
-
-enum ConvKind { CONV_FFMA = 0, CONV_TC_GATHER = 1, CONV_TC_SPLIT = 2 };
-
-// The tensor-core kernel that gathers fp32 rows itself exists for these shapes (the VM_TC list of launch_conv_tc).
-static bool has_tc_gather_kernel(const DenseLayer& L) {
-    if (L.tc_np == 0) return false;
-    const int ns = L.n_slots;
-    if (!L.tc_half) return L.cin == 8 && L.tc_np == 16 && (ns == 5 || ns == 7 || ns == 9);
-    if (L.cin == 16 && L.tc_np == 16) return ns == 5 || ns == 7 || ns == 9;
-    if ((L.cin == 16 && L.tc_np == 32) || (L.cin == 32 && (L.tc_np == 16 || L.tc_np == 32))) return ns == 7 || ns == 9;
-    return false;
-}
+enum ConvKind { CONV_FFMA = 0, CONV_TC_GATHER = 1, CONV_TC_SPLIT = 2, CONV_TC_STAGED = 3 };
 
 // Whether the kernel that runs layer L as `kind` honours ConvArgs::out_split. The tensor-core kernels write the split
 // layout when their tile is exactly as wide as the layer; the specialised FFMA kernels when the width is a multiple
 // of 8; the generic kernel never does.
 static bool producer_writes_split(const DenseLayer& L, ConvKind kind) {
+    if (kind == CONV_TC_STAGED) return L.cout % 8 == 0;
     if (kind != CONV_FFMA) return L.cout == L.tc_np;
     return has_fast_ffma_kernel(L.cin, L.cout) && L.cout % 8 == 0;
 }
 
-static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_frames, int max_rows, cudaStream_t s, ConvKind kind) {
+// Scratch of a chunk's tile plan (tile_plan.cuh): neighbour positions per row, halo lists per super-tile.
+static st::PlanOut ensure_tile_plan(Lane& lane, size_t rows_cap, size_t supertiles_cap) {
+    lane.d_nbl.ensure(rows_cap * STAGED_NBL_STRIDE + 64);
+    lane.d_halo_rows.ensure(supertiles_cap * STAGED_HALO + 64);
+    lane.d_halo_count.ensure(supertiles_cap + 64);
+    return st::PlanOut{lane.d_nbl.p, lane.d_halo_rows.p, lane.d_halo_count.p};
+}
+
+static void launch_conv(vm_engine* e, const DenseLayer& L, ConvArgs a, int n_frames, int max_rows, cudaStream_t s, ConvKind kind, const StagedPlan& plan) {
     a.weights     = L.d_weights;
     a.biases      = L.d_weights + static_cast<size_t>(L.n_slots) * L.cin * L.coutp;
     a.n_slots     = L.n_slots;
     a.activation  = L.activation;
-    dim3 grid(1, n_frames);
     begin_stage(e, s, L.stage.c_str());
-    if (kind == CONV_TC_SPLIT && launch_conv_tc_split(e, L, a, n_frames, max_rows, s)) {}
-    else if (kind == CONV_TC_GATHER && launch_conv_tc(e, L, a, n_frames, max_rows, s)) {}
-    else if (!launch_conv_fast(L, a, grid, max_rows, s)) {
-        dim3 g((max_rows + CONV_THREADS - 1) / CONV_THREADS, n_frames);
-        k_graph_conv_generic<<<g, CONV_THREADS, 0, s>>>(a, L.cin, L.cout, L.coutp);
+    if (kind == CONV_TC_STAGED && launch_conv_staged(L, a, plan, n_frames, max_rows, e->d_abort, e->tc_wait_limit, s)) {}
+    else if ((kind == CONV_TC_SPLIT || kind == CONV_TC_STAGED) && launch_conv_tc_split(L, a, n_frames, max_rows, e->d_abort, e->tc_wait_limit, s)) {}
+    else if (kind == CONV_TC_GATHER && launch_conv_tc_gather(L, a, n_frames, max_rows, e->d_abort, e->tc_wait_limit, s)) {}
+    else {
+        launch_conv_ffma(L, a, n_frames, max_rows, s);
     }
     VM_CUDA(cudaGetLastError());
     end_stage(e, s);
@@ -474,20 +261,29 @@ static void run_network(vm_engine* e,
                         float* out_final,
                         bool final_global,
                         int feature_stride) {
-    // Which kernel runs each layer. Tensor cores where the contraction is dense enough to pay (mode 1, the default:
-    // C_in x C_out >= 512), wherever a kernel exists (mode 2), never (mode 0). A tensor-core layer whose producer can
-    // write the split layout is fed by plain copies (CONV_TC_SPLIT); otherwise it gathers and splits fp32 itself.
+    // Which kernel runs each layer (VMCUDA_TC: 0 = CUDA cores only; 1, the default, and 2 = tensor cores too).
+    // A 16- or 32-channel layer whose producer can write the split layout runs as a staged layer (conv_staged.cuh,
+    // VMCUDA_STAGED=0 turns it off). Otherwise the tcgen05 kernels take a layer when its contraction is dense enough to
+    // pay (mode 1: C_in x C_out >= 512) or whenever one exists (mode 2): fed by plain copies from the split layout
+    // (CONV_TC_SPLIT) or gathering and splitting fp32 themselves (CONV_TC_GATHER).
     const size_t n_layers = e->layers.size();
     std::vector<ConvKind> kind(n_layers, CONV_FFMA);
     for (size_t l = 0; l < n_layers; ++l) {
         const DenseLayer& L = e->layers[l];
-        if (!e->use_tc || L.tc_np == 0 || n_frames > tc::MAX_FRAMES) continue;
+        if (!e->use_tc || L.tc_np == 0 || L.n_slots == 1 || n_frames > TC_MAX_FRAMES) continue;
+        const bool producer_can_split = l > 0 && producer_writes_split(e->layers[l - 1], kind[l - 1]) && !e->tc_no_split;
+        // the staged kernel wherever it exists (it writes features, not results: never the last layer)
+        if (e->staged && lane.plan_valid && producer_can_split && has_staged_kernel(L) && l + 1 < n_layers) {
+            kind[l] = CONV_TC_STAGED;
+            continue;
+        }
+        // the tcgen05 kernels where the contraction is dense enough for them to pay (mode 1) or wherever they exist (mode 2)
         if (e->tc_mode == 1 && L.cin * L.cout < e->tc_min_product) continue;
-        const bool producer_can_split = l > 0 && L.n_slots > 1 && producer_writes_split(e->layers[l - 1], kind[l - 1]);
-        if (has_tc_split_kernel(L) && producer_can_split && !e->tc_no_split) kind[l] = CONV_TC_SPLIT;
-        else if (L.n_slots > 1 && has_tc_gather_kernel(L)) kind[l] = CONV_TC_GATHER;
+        if (has_tc_split_kernel(L) && producer_can_split) kind[l] = CONV_TC_SPLIT;
+        else if (has_tc_gather_kernel(L)) kind[l] = CONV_TC_GATHER;
         // anything else (dense-only layers, shapes without a tensor-core instantiation) stays on the FFMA kernels
     }
+    const StagedPlan plan{lane.d_nbl.p, lane.d_halo_rows.p, lane.d_halo_count.p};
     int cur = 0;
     for (size_t l = 0; l < n_layers; ++l) {
         const bool last = l + 1 == n_layers;
@@ -502,9 +298,9 @@ static void run_network(vm_engine* e,
         a.in_stride    = feature_stride;
         a.out_stride   = feature_stride;
         a.out_planar   = (!last && e->layers[l].cout % 4 == 0) ? 1 : 0;
-        a.out_split    = (!last && kind[l + 1] == CONV_TC_SPLIT) ? 1 : 0;
+        a.out_split    = (!last && (kind[l + 1] == CONV_TC_SPLIT || kind[l + 1] == CONV_TC_STAGED)) ? 1 : 0;
         a.range_flag   = e->d_abort;
-        launch_conv(e, e->layers[l], a, n_frames, max_rows, lane.stream, kind[l]);
+        launch_conv(e, e->layers[l], a, n_frames, max_rows, lane.stream, kind[l], plan);
         cur ^= 1;
     }
 }
@@ -583,6 +379,9 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
     lane.d_ranges.ensure(3 * n_ranges_total + 4);
 
     int64_t cand_total = 0, node_total = 0, bsp_total = 0, image_total = 0;
+    const int plan_st     = STAGED_ST;
+    size_t supertiles_cap = 0;
+    lane.plan_valid       = false;
     int32_t max_cand = 0;
     bool any_device_lookup = false, any_host_ranges = false;
     size_t range_cursor = 0;
@@ -606,6 +405,7 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
             bsp_total += fr.mesh->n_bsp;
         }
         cand_total += nc;
+        supertiles_cap += static_cast<size_t>((nc + 1 + plan_st - 1) / plan_st);
         node_total += fr.mesh->n_nodes;
         max_cand = std::max<int32_t>(max_cand, static_cast<int32_t>(nc));
         if (classify && !fr.image_on_device) image_total += (image_bytes(fr) + 255) & ~size_t(255);
@@ -650,20 +450,37 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
         lane.d_images.ensure(image_total + 256);
     }
 
-    // images: host frames go through the lane's device buffer, device frames are read in place
+    // images: host frames go through the lane's device buffer, device frames are read in place. Frames that follow
+    // one another in host memory (a caller's ring of camera buffers, the rows of one big array) travel as ONE copy:
+    // sixteen 5 MB copies per chunk cost measurably more host time and bus turn-around than one 84 MB copy.
     if (classify) {
         size_t cursor = 0;
+        const uint8_t* run_src = nullptr;
+        size_t run_dst = 0, run_bytes = 0;
+        auto flush = [&] {
+            if (run_bytes > 0) VM_CUDA(cudaMemcpyAsync(lane.d_images.p + run_dst, run_src, run_bytes, cudaMemcpyHostToDevice, s));
+            run_bytes = 0;
+        };
         for (int f = f0; f < f1; ++f) {
             const vm_frame& fr = frames[f];
             FrameParams& p     = lane.h_frames.p[f - f0];
-            if (fr.image_on_device) { p.image = static_cast<const uint8_t*>(fr.image); }
-            else {
-                const size_t bytes = image_bytes(fr);
-                VM_CUDA(cudaMemcpyAsync(lane.d_images.p + cursor, fr.image, bytes, cudaMemcpyHostToDevice, s));
-                p.image = lane.d_images.p + cursor;
-                cursor += (bytes + 255) & ~size_t(255);
+            if (fr.image_on_device) {
+                p.image = static_cast<const uint8_t*>(fr.image);
+                continue;
             }
+            const size_t bytes = image_bytes(fr);
+            const uint8_t* src = static_cast<const uint8_t*>(fr.image);
+            if (run_bytes > 0 && src == run_src + run_bytes && cursor == run_dst + run_bytes) { run_bytes += bytes; }
+            else {
+                flush();
+                run_src   = src;
+                run_dst   = cursor;
+                run_bytes = bytes;
+            }
+            p.image = lane.d_images.p + cursor;
+            cursor += (bytes + 255) & ~size_t(255);
         }
+        flush();
     }
     VM_CUDA(cudaMemcpyAsync(lane.d_frames.p, lane.h_frames.p, sizeof(FrameParams) * nf, cudaMemcpyHostToDevice, s));
     if (n_ranges_total > 0) {
@@ -713,9 +530,17 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
         dim3 g((max_rows + ROW_THREADS - 1) / ROW_THREADS, nf);
         const int N = frames[f0].mesh->n_neighbours;
         begin_stage(e, s, "remap_neighbours");
-        if (N == 4) k_remap<4><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_gi.p, lane.d_node_rank.p, e->d_nb.p);
-        else if (N == 6) k_remap<6><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_gi.p, lane.d_node_rank.p, e->d_nb.p);
-        else k_remap<8><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_gi.p, lane.d_node_rank.p, e->d_nb.p);
+        // the staged layer kernels want a tile plan of the chunk: the remap makes it while it has the indices in hand
+        const bool with_plan = classify && e->staged && e->use_tc && e->may_stage && nf <= TC_MAX_FRAMES;
+        const st::PlanOut plan = with_plan ? ensure_tile_plan(lane, static_cast<size_t>(rows_cap), supertiles_cap) : st::PlanOut{nullptr, nullptr, nullptr};
+#define VM_REMAP(NN)                                                                                                                    \
+    if (N == NN) {                                                                                                                      \
+        if (with_plan) k_remap<NN, true><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_gi.p, lane.d_node_rank.p, e->d_nb.p, plan); \
+        else k_remap<NN, false><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_gi.p, lane.d_node_rank.p, e->d_nb.p, plan); \
+    }
+        VM_REMAP(4) VM_REMAP(6) VM_REMAP(8)
+#undef VM_REMAP
+        lane.plan_valid = with_plan;
         VM_CUDA(cudaGetLastError());
         end_stage(e, s);
         if (classify) {
@@ -826,7 +651,7 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
         bool host_images = false;
         for (int f = 0; f < n_frames; ++f) host_images = host_images || (classify && !frames[f].image_on_device);
         const int64_t max_chunk_candidates = (e->chunk_override || host_images) ? e->chunk_candidates : 4 * e->chunk_candidates;
-        const int max_chunk_frames         = (e->chunk_override || host_images) ? e->chunk_frames : std::min(4 * e->chunk_frames, static_cast<int>(tc::MAX_FRAMES));
+        const int max_chunk_frames         = (e->chunk_override || host_images) ? e->chunk_frames : std::min(4 * e->chunk_frames, static_cast<int>(TC_MAX_FRAMES));
         int f0 = 0, chunk = 0;
         Lane* prev = nullptr;
         std::vector<Lane*> order;
@@ -865,17 +690,17 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
             if (e->lanes[l].busy && e->lanes[l].stream != last_stream) VM_CUDA(cudaStreamWaitEvent(last_stream, e->lanes[l].ev_done, 0));
         }
         VM_CUDA(cudaMemcpyAsync(e->h_abort, e->d_abort, sizeof(int32_t), cudaMemcpyDeviceToHost, last_stream));
-        for (int l = 0; l < n_lanes; ++l) {
-            VM_CUDA(cudaStreamSynchronize(e->lanes[l].stream));
-            e->lanes[l].busy = false;
-        }
-        if (*e->h_abort == tc::ABORT_TC_RANGE && e->use_tc) {
+        // the last stream has waited for every other lane: one event behind the flag's copy marks the end of the batch
+        VM_CUDA(cudaEventRecord(e->ev_batch_done, last_stream));
+        VM_CUDA(cudaEventSynchronize(e->ev_batch_done));
+        for (int l = 0; l < n_lanes; ++l) e->lanes[l].busy = false;
+        if (*e->h_abort == ABORT_TC_RANGE && e->use_tc) {
             // a feature value beyond the range of the fp16 split: this engine goes back to the FFMA kernels for good and
             // the batch is computed again
             e->use_tc = false;
             return run_batch(e, frames, n_frames, flags, out);
         }
-        if (*e->h_abort == tc::ABORT_TC_TIMEOUT) return fail(VM_ERR_DEVICE_ABORT, "a tensor-core kernel gave up waiting on an mbarrier");
+        if (*e->h_abort == ABORT_TC_TIMEOUT) return fail(VM_ERR_DEVICE_ABORT, "a tensor-core kernel gave up waiting on an mbarrier");
         if (*e->h_abort != 0) return fail(VM_ERR_DEVICE_ABORT, "a kernel gave up on a bounded loop (BSP deeper than 128 levels)");
 
         if (e->timing) {
@@ -989,18 +814,24 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
         }
         if (const char* v = std::getenv("VMCUDA_TC_MIN_PRODUCT")) e->tc_min_product = std::atoi(v);
         if (const char* v = std::getenv("VMCUDA_TC_NO_SPLIT")) e->tc_no_split = std::atoi(v) != 0;
+        if (const char* v = std::getenv("VMCUDA_STAGED")) e->staged = std::atoi(v) != 0;
+        if (const char* v = std::getenv("VMCUDA_BLOCKING_SYNC")) e->blocking_sync = std::atoi(v) != 0;
         if (const char* v = std::getenv("VMCUDA_LANES")) e->n_lanes = std::min(MAX_LANES, std::max(1, std::atoi(v)));
         for (int l = 0; l < MAX_LANES; ++l) {
             Lane& lane = e->lanes[l];
             VM_CUDA(cudaStreamCreateWithFlags(&lane.stream, cudaStreamNonBlocking));
             VM_CUDA(cudaEventCreateWithFlags(&lane.ev_staged, cudaEventDisableTiming));
             VM_CUDA(cudaEventCreateWithFlags(&lane.ev_scan, cudaEventDisableTiming));
-            VM_CUDA(cudaEventCreateWithFlags(&lane.ev_offsets, cudaEventDisableTiming));
-            VM_CUDA(cudaEventCreateWithFlags(&lane.ev_done, cudaEventDisableTiming));
+            // the two events the host waits on: spinning (lowest latency) or, with VMCUDA_BLOCKING_SYNC=1, sleeping - for
+            // boxes where several engines' host threads share few cores
+            const unsigned wait_flags = cudaEventDisableTiming | (e->blocking_sync ? cudaEventBlockingSync : 0);
+            VM_CUDA(cudaEventCreateWithFlags(&lane.ev_offsets, wait_flags));
+            VM_CUDA(cudaEventCreateWithFlags(&lane.ev_done, wait_flags));
         }
         VM_CUDA(cudaEventCreate(&e->ev_timer_start));
         VM_CUDA(cudaEventCreate(&e->ev_timer_stop));
         VM_CUDA(cudaEventCreateWithFlags(&e->ev_batch_start, cudaEventDisableTiming));
+        VM_CUDA(cudaEventCreateWithFlags(&e->ev_batch_done, cudaEventDisableTiming | (e->blocking_sync ? cudaEventBlockingSync : 0)));
         VM_CUDA(cudaMalloc(reinterpret_cast<void**>(&e->d_abort), sizeof(int32_t)));
         VM_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&e->h_abort), sizeof(int32_t), cudaHostAllocDefault));
         int l = 0;
@@ -1073,6 +904,7 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
             }
         }
         e->n_classes = e->layers.empty() ? 0 : e->layers.back().cout;
+        for (size_t l = 1; l + 1 < e->layers.size(); ++l) e->may_stage = e->may_stage || has_staged_kernel(e->layers[l]);
     }
     catch (const CudaFailure& f) {
         cudaGetLastError();
@@ -1116,6 +948,9 @@ void vm_engine_destroy(vm_engine* e) {
         lane.d_feat[0].release();
         lane.d_feat[1].release();
         lane.d_images.release();
+        lane.d_nbl.release();
+        lane.d_halo_rows.release();
+        lane.d_halo_count.release();
         if (lane.stream) cudaStreamDestroy(lane.stream);
         if (lane.ev_staged) cudaEventDestroy(lane.ev_staged);
         if (lane.ev_scan) cudaEventDestroy(lane.ev_scan);
@@ -1136,6 +971,7 @@ void vm_engine_destroy(vm_engine* e) {
     if (e->ev_timer_start) cudaEventDestroy(e->ev_timer_start);
     if (e->ev_timer_stop) cudaEventDestroy(e->ev_timer_stop);
     if (e->ev_batch_start) cudaEventDestroy(e->ev_batch_start);
+    if (e->ev_batch_done) cudaEventDestroy(e->ev_batch_done);
     cudaFree(e->d_abort);
     cudaFreeHost(e->h_abort);
     delete e;
@@ -1313,11 +1149,19 @@ vm_status vm_network(vm_engine* e, const float* input, const int32_t* neighbourh
             // the layers ping-pong over the feature buffers, so a second attempt needs the input again
             VM_CUDA(cudaMemcpyAsync(lane.d_feat[0].p, input, sizeof(float) * rows * 4, cudaMemcpyHostToDevice, lane.stream));
             VM_CUDA(cudaMemsetAsync(e->d_abort, 0, sizeof(int32_t), lane.stream));
+            lane.plan_valid = false;
+            if (e->staged && e->use_tc && e->may_stage) {
+                const st::PlanOut plan = ensure_tile_plan(lane, rows, (rows + STAGED_ST - 1) / STAGED_ST + 1);
+                ++e->launches;
+                launch_tile_plan_kernel(n_neighbours, e->d_offsets.p, e->d_nb.p, plan.nbl, plan.halo_rows, plan.halo_count, 0, 1, n_rows, lane.stream);
+                VM_CUDA(cudaGetLastError());
+                lane.plan_valid = true;
+            }
             run_network(e, lane, e->d_offsets.p, e->d_nb.p, n_neighbours, 0, 1, n_rows, e->d_cls.p, true, n_rows);
             VM_CUDA(cudaMemcpyAsync(out, e->d_cls.p, sizeof(float) * rows * e->n_classes, cudaMemcpyDeviceToHost, lane.stream));
             VM_CUDA(cudaMemcpyAsync(e->h_abort, e->d_abort, sizeof(int32_t), cudaMemcpyDeviceToHost, lane.stream));
             VM_CUDA(cudaStreamSynchronize(lane.stream));
-            if (*e->h_abort == tc::ABORT_TC_RANGE && e->use_tc) {
+            if (*e->h_abort == ABORT_TC_RANGE && e->use_tc) {
                 e->use_tc = false;  // a value beyond the fp16 split's range: recompute with the FFMA kernels
                 continue;
             }
@@ -1423,9 +1267,10 @@ vm_status vm_project_static(vm_engine* e,
         k_scatter<<<dim3(blocks, 1), SELECT_THREADS, 0, s>>>(d_frame, d_cand_px, d_cand_node, d_blocks, d_cells, 0,
                                                              reinterpret_cast<float2*>(d_px), d_gi, d_rank);
         dim3 g((mesh->n_nodes + 1 + ROW_THREADS - 1) / ROW_THREADS, 1);
-        if (mesh->n_neighbours == 4) k_remap<4><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb);
-        else if (mesh->n_neighbours == 6) k_remap<6><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb);
-        else k_remap<8><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb);
+        const st::PlanOut no_plan{nullptr, nullptr, nullptr};
+        if (mesh->n_neighbours == 4) k_remap<4, false><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb, no_plan);
+        else if (mesh->n_neighbours == 6) k_remap<6, false><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb, no_plan);
+        else k_remap<8, false><<<g, ROW_THREADS, 0, s>>>(d_frame, d_cells, 0, d_gi, d_rank, d_nb, no_plan);
         VM_CUDA(cudaGetLastError());
         e->launches += 5;
         if (d_n_points != nullptr) VM_CUDA(cudaMemcpyAsync(d_n_points, d_cells + 1, sizeof(int32_t), cudaMemcpyDeviceToDevice, s));

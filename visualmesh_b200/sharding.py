@@ -23,13 +23,22 @@ def round_robin(items: Sequence, rank: int, world: int) -> List:
     return list(items[rank::world])
 
 
-def reduce_timing(dist, elapsed_s: float, frames: int, points: int, device=None):
-    """(max elapsed over ranks, total frames, total points). `dist` is torch.distributed or None for one process."""
+def max_over_ranks(dist, x: float, device=None) -> float:
+    """The largest x of all ranks (a timed region lasts as long as its slowest rank). `dist` is torch.distributed, or
+    None for one process; `device` is where the one-element tensor lives ("cuda" for NCCL, None for gloo)."""
     if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
-        return elapsed_s, frames, points
+        return float(x)
     import torch
-    t = torch.tensor([elapsed_s], dtype=torch.float64, device=device)
-    c = torch.tensor([float(frames), float(points)], dtype=torch.float64, device=device)
+    t = torch.tensor([x], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dist.all_reduce(c, op=dist.ReduceOp.SUM)
-    return float(t[0]), int(c[0]), int(c[1])
+    return float(t.item())
+
+
+def sum_over_ranks(dist, x: float, device=None) -> float:
+    """The sum of x over all ranks (whole-job counts: frames, points, bytes)."""
+    if dist is None or not dist.is_initialized() or dist.get_world_size() == 1:
+        return float(x)
+    import torch
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
