@@ -45,10 +45,18 @@ from visualmesh_b200 import workloads as W  # noqa: E402
 # DRAM traffic per row of the dominant kernels from their ncu captures (dram__bytes_read + dram__bytes_write over the
 # rows of the captured launch); traffic grows in proportion to the rows, so it is scaled to the bench's launches.
 NCU_TRAFFIC_BYTES_PER_ROW = {
-    (16, 16): 107.4,  # profiles/graph_conv_staged_16x16_cfg1_16frames.md: 119.0 MB over 1,108,261 rows
+    (16, 16): 109.6,  # profiles/graph_conv_staged_16x16_cfg1_16frames.md: 121.5 MB over 1,108,261 rows
     (32, 32): 250.4,  # profiles/graph_conv_tc_tmem_32x32_cfg3_1frame.md: 233.3 MB over 931,718 rows
 }
-KERNEL_OF_LAYER = {16: "st::k_graph_conv_mma (staged, mma.sync)", 32: "tc::k_graph_conv_tc_tmem (tcgen05)"}
+
+
+def _kernel_of_layer(cin, cout):
+    """Which kernel the engine's default policy runs a gather layer on (visualmesh_b200/csrc/engine.cu, run_network)."""
+    if cin == 16 and cout in (8, 16, 32):
+        return "st::k_graph_conv_mma (shared-memory windows, ldmatrix gather, mma.sync)"
+    if cin in (16, 32) and cout in (16, 32) and cin * cout >= 512:
+        return "tc::k_graph_conv_tc_tmem (tcgen05, A operand in tensor memory)"
+    return "k_graph_conv_cw (FFMA)"
 
 
 def _peaks():
@@ -381,7 +389,7 @@ def _roofline(arm, stage_total, stage_launches, rows_per_step, steps):
     top_s = 1e-3 * stage_total[top]
     achieved = bytes_per_row * rows_total / top_s / 1e9
     gpu_ms_total = sum(stage_total.values())
-    return {"bound": "hbm", "kernel": f"graph_conv {cin}->{cout}: " + KERNEL_OF_LAYER.get(cin, "k_graph_conv_cw (FFMA)"),
+    return {"bound": "hbm", "kernel": f"graph_conv {cin}->{cout}: " + _kernel_of_layer(cin, cout),
             "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
             "traffic": (NCU_TRAFFIC_BYTES_PER_ROW[(cin, cout)] * rows_total / stage_launches[top])
             if (cin, cout) in NCU_TRAFFIC_BYTES_PER_ROW else None,
@@ -394,7 +402,7 @@ def _roofline(arm, stage_total, stage_launches, rows_per_step, steps):
 def _other_config(cfg, args, local_rank, parity):
     """One of the other benchmark configurations on one GPU: device-resident and end-to-end frames/s, its dominant
     kernel, and the reference CPU engine's rate on the same box (from the parity run over the same configuration)."""
-    n = {0: 64, 2: 32, 3: 32}[cfg]
+    n = 64  # frames per step, as for the headline (the configurations' own 1 / 32 / 32 frames repeat their generator)
     wl = W.config(cfg, seed=args.seed, n_frames=n)
     arm = Arm(wl, wl.frames, local_rank, args.instances)
     arm.warm(3)

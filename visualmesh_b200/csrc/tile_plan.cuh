@@ -16,7 +16,7 @@ namespace st {
 
     constexpr int ST               = 256;     // rows of a super-tile = threads of the block that plans it
     constexpr int HALO             = 192;     // halo slots of a super-tile
-    constexpr int HASH_SIZE        = 2048;    // open-addressing table of a super-tile's outside rows
+    constexpr int HASH_SIZE        = 1024;    // open-addressing table of a super-tile's outside rows
     constexpr uint32_t NBL_GLOBAL  = 0xFFFFu; // neighbour position: not staged, fetch from global memory
     constexpr int NBL_STRIDE       = 8;       // 16-bit positions per row (N <= 8), one 16-byte load
 
@@ -33,14 +33,14 @@ namespace st {
     };
 
     __device__ __forceinline__ uint32_t hash_row(int32_t v) {
-        return (static_cast<uint32_t>(v) * 2654435761u) >> 21;  // top 11 bits: [0, HASH_SIZE)
+        return (static_cast<uint32_t>(v) * 2654435761u) >> 22;  // top 10 bits: [0, HASH_SIZE)
     }
 
     // Called by all ST threads of a block for super-tile blockIdx.x of frame f (the f-th of the launch, frames f0 ...):
     // thread tid holds the frame-local neighbour indices idx[0..N) of row t0 + tid (valid: the row exists).
     template <int N>
     __device__ __forceinline__ void plan_super_tile(const int (&idx)[N], bool valid, int t0, int f, const int32_t* offsets, int f0, const PlanOut& out) {
-        static_assert(HASH_SIZE % ST == 0 && HASH_SIZE == 2048, "table entries are dealt evenly to the threads");
+        static_assert(HASH_SIZE % ST == 0 && HASH_SIZE == 1024, "table entries are dealt evenly to the threads, the hash has 10 bits");
         static_assert(N <= NBL_STRIDE, "one 16-byte row of positions");
         constexpr int PER = HASH_SIZE / ST;
         __shared__ int32_t keys[HASH_SIZE];
