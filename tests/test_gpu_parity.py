@@ -289,6 +289,66 @@ def test_example_model_through_the_cpp_drop_in_engine():
         assert rep.ok and rep.indices_exact, str(rep)
 
 
+# ---- staged layers (tile plan, shared-memory windows, warp-level MMAs) -----------------------------------------------
+
+@needs_ref
+def test_staged_layers_on_the_dense_mesh_with_halo_overflow():
+    """A 16-wide network on configuration 3's dense Ring8 mesh (0.93 M rows, 9 slots): a few percent of its 256-row
+    super-tiles have more outside rows than halo slots, so staged neighbours and neighbours fetched from global memory
+    mix inside one launch. The whole call against the reference CPU engine, and staged against not staged."""
+    import os
+    wl = W.config(3, n_frames=1)
+    fr = wl.frames[0]
+    net = W.make_network(29, 8, [16, 16, 8, 2])
+    ref_mesh = R.RefMesh(fr.mesh)
+    image = fr.image()
+    ref = ref_mesh.classify(net, fr.Hoc, fr.lens, image, fr.format)
+    mesh = Mesh.from_spec(fr.mesh)
+    outs = {}
+    for staged in ("1", "0"):
+        os.environ["VMCUDA_STAGED"] = staged
+        try:
+            engine = Engine(net)
+        finally:
+            os.environ.pop("VMCUDA_STAGED")
+        outs[staged] = engine.run_batch([FrameInput(mesh, fr.Hoc, fr.lens, image, fr.format, None)]).frame(0)
+        rep = P.compare(outs[staged], ref, fr.lens.dimensions)
+        print(f"cfg3 mesh, 16-wide network, staged={staged}: {rep}")
+        assert rep.ok and rep.n_ref > 900000, str(rep)
+        engine.close()
+    d = np.abs(outs["1"].classifications.astype(np.float64) - outs["0"].classifications.astype(np.float64)).max()
+    assert d <= P.TOL_CLS / 4
+
+
+def test_staged_and_unstaged_layers_agree_on_a_batch_of_unequal_frames(cases):
+    """Frames of different sizes in one launch (super-tiles never straddle frames; the last super-tile of a frame is
+    partial)."""
+    import os
+    case = cases["ring6_equisolid_rgba"]
+    net = W.make_network(33, 6, [16, 16, 16, 8, 3])
+    mesh_args = (case.rays, case.nbrs, case.bsp)
+    order = [0, 2, 1, 0, 1, 2, 2]
+    results = {}
+    for staged in ("1", "0"):
+        os.environ["VMCUDA_STAGED"] = staged
+        try:
+            engine = Engine(net)
+        finally:
+            os.environ.pop("VMCUDA_STAGED")
+        mesh = Mesh.from_arrays(*mesh_args)
+        frames = [FrameInput(mesh, case.frames[i]["Hoc"], case.lens, case.frames[i]["image"], case.format, None) for i in order]
+        batch = engine.run_batch(frames)
+        results[staged] = [batch.frame(f) for f in range(len(order))]
+        for f, i in enumerate(order):
+            fr = case.frames[i]
+            want = O.classify(case.rays, case.nbrs, fr["ranges"], net, fr["Hoc"], case.lens, fr["image"], case.format)
+            assert P.compare(results[staged][f], want, case.lens.dimensions).ok
+        engine.close()
+    for a, b in zip(results["1"], results["0"]):
+        assert np.array_equal(a.global_indices, b.global_indices)
+        assert np.abs(a.classifications.astype(np.float64) - b.classifications.astype(np.float64)).max() <= P.TOL_CLS / 4
+
+
 # ---- tensor-core graph convolution (tcgen05) ---------------------------------------------------------------------------
 
 def _engine_with_tc(network, mode):
