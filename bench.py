@@ -421,7 +421,7 @@ def _other_config(cfg, args, local_rank, parity):
                                "share_of_gpu_time": roof["share_of_gpu_time"]}}
     if parity and parity.get("reference_seconds"):
         out["cpu_baseline"] = {"value": parity["frames"] / parity["reference_seconds"], "unit": "frames/s",
-                               "cores": os.cpu_count() or 1, "kind": "reference",
+                               "cores": min(os.cpu_count() or 1, parity["frames"]), "kind": "reference",
                                "sample": f"the {parity['frames']} frames of the parity check, one pass"}
     arm.close()
     return out

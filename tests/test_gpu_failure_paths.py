@@ -2,7 +2,7 @@
 
 Every device-side loop or wait that depends on data or on another agent is bounded; when the bound runs out the kernel
 raises a flag, leaves through its normal tear-down, and the call returns VM_ERR_DEVICE_ABORT. The tests make the bound
-run out with well-formed but useless inputs (a BSP whose root names itself as its child, a poll limit of zero) and then
+run out with well-formed but useless inputs (a BSP with a cycle, a poll limit of zero) and then
 use the same engine again.
 """
 import os
@@ -41,16 +41,18 @@ def _random_rows(n, n_neighbours, seed):
     return x, nb
 
 
-def test_bsp_that_never_reaches_a_leaf_stops_after_128_levels():
-    """The device lookup walks the BSP from the root (cpp/visualmesh/mesh.hpp:559-583). A root whose children are
-    itself passes the upload's range checks but has no leaf: the walk stops at its depth limit, the call reports
-    VM_ERR_DEVICE_ABORT, and the engine then runs the intact mesh as if nothing had happened."""
+def test_bsp_with_a_cycle_stops_after_128_levels():
+    """The device lookup follows the BSP between the root and the leaves (cpp/visualmesh/mesh.hpp:559-583). An inner
+    element whose children are the root passes the upload's range checks but closes a cycle: the walk stops at its
+    depth limit, the call reports VM_ERR_DEVICE_ABORT, and the engine then runs the intact mesh as if nothing had
+    happened."""
     case = G.Case("ring6_equisolid_rgba")
     fr = case.frames[0]
     engine = Engine(case.network)
     good = Mesh.from_arrays(case.rays, case.nbrs, case.bsp)
     children = case.bsp[1].copy()
-    children[0] = (0, 0)
+    inner = [i for i in range(1, len(children)) if children[i][0] >= 0]
+    children[inner[0]] = (0, 0)
     looped = Mesh.from_arrays(case.rays, case.nbrs, (case.bsp[0], children, case.bsp[2]))
     with pytest.raises(VisualMeshError) as e:
         engine.run_batch([FrameInput(looped, fr["Hoc"], case.lens, fr["image"], case.format, None)])
