@@ -245,8 +245,21 @@ namespace st {
 
         if (warp == WARPS) {
             // ================= loader warp: one window ahead of the compute warps per buffer =================
+            // The halo list of a super-tile (its length, then this lane's entries) is read one super-tile ahead, while
+            // the loader waits for a buffer anyway: the copies of a window then start the moment its buffer is free
+            // instead of two dependent trips to global memory later.
+            constexpr int PER_LANE = (HALO + 31) / 32;
+            int n_halo = 0;
+            int32_t halo_row[PER_LANE];
+            auto fetch_halo_list = [&](int st) {
+                n_halo                = __ldg(plan.halo_count + st);
+                const int32_t* h_rows = plan.halo_rows + static_cast<size_t>(st) * HALO;
+#pragma unroll
+                for (int k = 0; k < PER_LANE; ++k) halo_row[k] = __ldg(h_rows + min(lane + 32 * k, HALO - 1));  // entries past n_halo are never used
+            };
             uint32_t n = 0;
             bool ok    = true;
+            if (static_cast<int>(blockIdx.x) < total_st) fetch_halo_list(blockIdx.x);
             for (int s = blockIdx.x; s < total_st; s += gridDim.x, ++n) {
                 const uint32_t b = n & 1u;
                 // every compute warp must be done with the super-tile that used this buffer before
@@ -266,13 +279,16 @@ namespace st {
                                   static_cast<uint32_t>(own * 16), bar);
                     }
                 }
-                const int n_halo      = __ldg(plan.halo_count + s);
-                const int32_t* h_rows = plan.halo_rows + static_cast<size_t>(s) * HALO;
-                for (int h = lane; h < n_halo; h += 32) {
-                    const size_t src_row = static_cast<size_t>(__ldg(h_rows + h));
 #pragma unroll
-                    for (int p = 0; p < ALLP; ++p) copy16(dst + p * PSTRIDE + (ST + h) * 16, in_bytes + (static_cast<size_t>(p) * a.in_stride + src_row) * 16);
+                for (int k = 0; k < PER_LANE; ++k) {
+                    const int h = lane + 32 * k;
+                    if (h < n_halo) {
+                        const size_t src_row = static_cast<size_t>(halo_row[k]);
+#pragma unroll
+                        for (int p = 0; p < ALLP; ++p) copy16(dst + p * PSTRIDE + (ST + h) * 16, in_bytes + (static_cast<size_t>(p) * a.in_stride + src_row) * 16);
+                    }
                 }
+                if (s + static_cast<int>(gridDim.x) < total_st) fetch_halo_list(s + gridDim.x);
                 copies_arrive(bar);
             }
             if (!ok) *failed = 1;
