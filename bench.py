@@ -45,7 +45,7 @@ from visualmesh_b200 import workloads as W  # noqa: E402
 # DRAM traffic per row of the dominant kernels from their ncu captures (dram__bytes_read + dram__bytes_write over the
 # rows of the captured launch); traffic grows in proportion to the rows, so it is scaled to the bench's launches.
 NCU_TRAFFIC_BYTES_PER_ROW = {
-    (16, 16): 109.6,  # profiles/graph_conv_staged_16x16_cfg1_16frames.md: 121.5 MB over 1,108,261 rows
+    (16, 16): 110.6,  # profiles/graph_conv_staged_16x16_cfg1_16frames.md: 122.6 MB over 1,108,261 rows
     (32, 32): 250.4,  # profiles/graph_conv_tc_tmem_32x32_cfg3_1frame.md: 233.3 MB over 931,718 rows
 }
 
