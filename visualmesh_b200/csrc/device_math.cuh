@@ -225,24 +225,28 @@ __device__ __forceinline__ float4 bayer_pixel(int x, int y, const uint8_t* image
                        __fmul_rn(static_cast<float>(b), s), __fmul_rn(255.0f, s));
 }
 
+// cpp/visualmesh/engine/cpu/pixel.hpp:44-58: the two formats of four bytes per pixel
+__device__ __forceinline__ float4 get_pixel_packed4(int x, int y, const uint8_t* image, int W, bool bgra) {
+    const float s    = static_cast<float>(1.0 / 255.0);
+    const uint8_t* c = image + (static_cast<size_t>(y) * W + x) * 4;
+    uchar4 v;
+    if ((reinterpret_cast<uintptr_t>(image) & 3) == 0) { v = __ldg(reinterpret_cast<const uchar4*>(c)); }
+    else {
+        v = make_uchar4(__ldg(c), __ldg(c + 1), __ldg(c + 2), __ldg(c + 3));
+    }
+    const float a0 = __fmul_rn(static_cast<float>(v.x), s);
+    const float a1 = __fmul_rn(static_cast<float>(v.y), s);
+    const float a2 = __fmul_rn(static_cast<float>(v.z), s);
+    const float a3 = __fmul_rn(static_cast<float>(v.w), s);
+    return bgra ? make_float4(a2, a1, a0, a3) : make_float4(a0, a1, a2, a3);
+}
+
 // cpp/visualmesh/engine/cpu/pixel.hpp:44-102
 __device__ __forceinline__ float4 get_pixel(int x, int y, const uint8_t* image, int W, int H, int cls) {
     const float s = static_cast<float>(1.0 / 255.0);
     switch (cls) {
         case FMT_RGBA:
-        case FMT_BGRA: {
-            const uint8_t* c = image + (static_cast<size_t>(y) * W + x) * 4;
-            uchar4 v;
-            if ((reinterpret_cast<uintptr_t>(image) & 3) == 0) { v = __ldg(reinterpret_cast<const uchar4*>(c)); }
-            else {
-                v = make_uchar4(__ldg(c), __ldg(c + 1), __ldg(c + 2), __ldg(c + 3));
-            }
-            const float a0 = __fmul_rn(static_cast<float>(v.x), s);
-            const float a1 = __fmul_rn(static_cast<float>(v.y), s);
-            const float a2 = __fmul_rn(static_cast<float>(v.z), s);
-            const float a3 = __fmul_rn(static_cast<float>(v.w), s);
-            return cls == FMT_RGBA ? make_float4(a0, a1, a2, a3) : make_float4(a2, a1, a0, a3);
-        }
+        case FMT_BGRA: return get_pixel_packed4(x, y, image, W, cls == FMT_BGRA);
         case FMT_RGB3:
         case FMT_BGR3: {
             const uint8_t* c = image + (static_cast<size_t>(y) * W + x) * 3;
@@ -259,18 +263,19 @@ __device__ __forceinline__ float4 get_pixel(int x, int y, const uint8_t* image, 
     }
 }
 
-// cpp/visualmesh/engine/cpu/pixel.hpp:116-144
-__device__ __forceinline__ float4 interpolate(float2 P, const uint8_t* image, int W, int H, int cls) {
+// cpp/visualmesh/engine/cpu/pixel.hpp:116-144; fetch(x, y) returns the pixel at integer coordinates
+template <class Fetch>
+__device__ __forceinline__ float4 interpolate_with(float2 P, int W, int H, Fetch fetch) {
     const float x = P.x;
     const float y = P.y;
     const int x1  = max(static_cast<int>(floorf(x)), 0);
     const int y1  = max(static_cast<int>(floorf(y)), 0);
     const int x2  = min(x1 + 1, W - 1);
     const int y2  = min(y1 + 1, H - 1);
-    const float4 Q1 = get_pixel(x1, y1, image, W, H, cls);
-    const float4 Q2 = get_pixel(x2, y1, image, W, H, cls);
-    const float4 Q3 = get_pixel(x1, y2, image, W, H, cls);
-    const float4 Q4 = get_pixel(x2, y2, image, W, H, cls);
+    const float4 Q1 = fetch(x1, y1);
+    const float4 Q2 = fetch(x2, y1);
+    const float4 Q3 = fetch(x1, y2);
+    const float4 Q4 = fetch(x2, y2);
     const float dx  = static_cast<float>(x2 - x1);
     const float dy  = static_cast<float>(y2 - y1);
     const float wx0 = __fdiv_rn(__fsub_rn(static_cast<float>(x2), x), dx);
@@ -283,6 +288,13 @@ __device__ __forceinline__ float4 interpolate(float2 P, const uint8_t* image, in
     const float4 out = make_float4(VM_BLEND(x), VM_BLEND(y), VM_BLEND(z), VM_BLEND(w));
 #undef VM_BLEND
     return out;
+}
+__device__ __forceinline__ float4 interpolate(float2 P, const uint8_t* image, int W, int H, int cls) {
+    return interpolate_with(P, W, H, [=](int x, int y) { return get_pixel(x, y, image, W, H, cls); });
+}
+// the same for an image that is known to be RGBA or BGRA: a fraction of the registers of the general sampler
+__device__ __forceinline__ float4 interpolate_packed4(float2 P, const uint8_t* image, int W, int H, bool bgra) {
+    return interpolate_with(P, W, H, [=](int x, int y) { return get_pixel_packed4(x, y, image, W, bgra); });
 }
 
 }  // namespace vm

@@ -545,8 +545,19 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
         end_stage(e, s);
         if (classify) {
             begin_stage(e, s, "sample_image");
-            k_sample<<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_px.p,
-                                               reinterpret_cast<float4*>(lane.d_feat[0].p));
+            bool packed4 = true;
+            for (int f = f0; f < f1; ++f) {
+                const int cls = format_class(frames[f].format);
+                packed4 &= cls == FMT_RGBA || cls == FMT_BGRA;
+            }
+            if (packed4) {
+                k_sample<true><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_px.p,
+                                                         reinterpret_cast<float4*>(lane.d_feat[0].p));
+            }
+            else {
+                k_sample<false><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_px.p,
+                                                          reinterpret_cast<float4*>(lane.d_feat[0].p));
+            }
             VM_CUDA(cudaGetLastError());
             end_stage(e, s);
             run_network(e, lane, e->d_offsets.p, e->d_nb.p, N, f0, nf, max_rows, e->d_cls.p, true, static_cast<int>(rows_cap));

@@ -100,13 +100,15 @@ __global__ void __launch_bounds__(SELECT_THREADS) k_select(const FrameParams* __
             int e = 0;
             int steps = 0;
             for (; steps < 128; ++steps) {
+                // both loads of a step are issued together: the walk is a chain of dependent loads, and the element's
+                // topology is in bounds whatever its state turns out to be
                 const uint8_t s = state[p.bsp_off + e];
+                const int4 t    = __ldg(p.bsp_topology + e);
                 if (s == BSP_INSIDE) break;
                 if (s == BSP_OUTSIDE) {
                     selected = false;
                     break;
                 }
-                const int4 t = __ldg(p.bsp_topology + e);
                 if (t.x < 0) {
                     test_fov = true;
                     break;
@@ -262,6 +264,9 @@ __global__ void __launch_bounds__(ROW_THREADS) k_remap(const FrameParams* __rest
 
 // ---- image sampling ----------------------------------------------------------------------------------------------
 // cpp/visualmesh/engine/cpu/engine.hpp:198-206: bilinear sample at every point, four -1 for the off-screen row.
+// PACKED4: every frame of the launch is RGBA or BGRA. The general sampler carries the 5x5 Bayer patch in its register
+// count (66), which holds it to three blocks per SM although it waits on memory; the packed one fills the SM.
+template <bool PACKED4>
 __global__ void __launch_bounds__(ROW_THREADS) k_sample(const FrameParams* __restrict__ frames,
                                                         const int32_t* __restrict__ offsets,
                                                         int32_t f0,
@@ -275,7 +280,12 @@ __global__ void __launch_bounds__(ROW_THREADS) k_sample(const FrameParams* __res
     if (i > n) return;
     const int local_row = start - offsets[f0] + blockIdx.y + i;
     float4 v            = make_float4(-1.0f, -1.0f, -1.0f, -1.0f);
-    if (i < n) { v = interpolate(out_px[start + i], p.image, p.dims[0], p.dims[1], format_class(p.format)); }
+    if (i < n) {
+        if (PACKED4) { v = interpolate_packed4(out_px[start + i], p.image, p.dims[0], p.dims[1], p.format == fcc('B', 'G', 'R', 'A')); }
+        else {
+            v = interpolate(out_px[start + i], p.image, p.dims[0], p.dims[1], format_class(p.format));
+        }
+    }
     features[local_row] = v;
 }
 
