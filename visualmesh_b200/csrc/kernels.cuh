@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(SELECT_THREADS) k_select(const FrameParams* __
             px   = project(cx, cy, cz, p);
             keep = on_screen_strict(px, p) && (!test_fov || cx > p.cos_fov);
         }
-        cand_px[p.cand_off + c]   = px;
+        if (keep) cand_px[p.cand_off + c] = px;  // the scatter reads the pixels of kept candidates only
         cand_node[p.cand_off + c] = keep ? g : -1;
     }
     const int n = __syncthreads_count(keep);
@@ -139,40 +139,60 @@ __global__ void __launch_bounds__(SELECT_THREADS) k_select(const FrameParams* __
 // ---- scan of the per-block counts --------------------------------------------------------------------------------
 // One block. Turns block_counts into exclusive block offsets relative to the chunk's first point and extends the
 // batch-wide offsets array: offsets[f0 + y + 1] for every frame y of the chunk, continuing from offsets[f0].
+// Each warp owns a contiguous run of the counts and walks it 32 at a time, so every load and store is one coalesced
+// line; the first pass sums the runs, the second redoes each run as a shuffle scan carried from line to line.
 __global__ void __launch_bounds__(1024) k_scan(int32_t* __restrict__ block_counts,
                                                int32_t n_blocks,
                                                int32_t blocks_per_frame,
                                                int32_t n_frames,
                                                int32_t* __restrict__ offsets,
                                                int32_t f0) {
-    __shared__ int32_t partial[1024];
+    __shared__ int32_t warp_base[33];
     const int t     = threadIdx.x;
-    const int per   = (n_blocks + 1023) / 1024;
-    const int begin = min(t * per, n_blocks);
-    const int end   = min(begin + per, n_blocks);
+    const int lane  = t & 31;
+    const int warp  = t >> 5;
+    const int lines = (n_blocks + 1023) / 1024;  // 32-count lines per warp
+    const int begin = min(warp * lines * 32, n_blocks);
+    const int end   = min(begin + lines * 32, n_blocks);
     int sum         = 0;
-    for (int i = begin; i < end; ++i) sum += block_counts[i];
-    partial[t] = sum;
+#pragma unroll 4
+    for (int i = begin + lane; i < end; i += 32) sum += block_counts[i];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    if (lane == 0) warp_base[warp + 1] = sum;
     __syncthreads();
-    // Hillis-Steele inclusive scan over the 1024 partials
-    for (int d = 1; d < 1024; d <<= 1) {
-        const int v = (t >= d) ? partial[t - d] : 0;
-        __syncthreads();
-        partial[t] += v;
-        __syncthreads();
+    if (warp == 0) {
+        // exclusive scan of the 32 run totals; warp_base[32] keeps the grand total
+        int v = warp_base[lane + 1];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, v, d);
+            if (lane >= d) v += u;
+        }
+        warp_base[lane + 1] = v;
+        if (lane == 0) warp_base[0] = 0;
     }
-    int run = partial[t] - sum;
-    for (int i = begin; i < end; ++i) {
-        const int v     = block_counts[i];
-        block_counts[i] = run;
-        run += v;
+    __syncthreads();
+    const int total = warp_base[32];
+    int run         = warp_base[warp];
+    for (int i0 = begin; i0 < end; i0 += 32) {
+        const int i = i0 + lane;
+        const int c = (i < end) ? block_counts[i] : 0;
+        int v       = c;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, v, d);
+            if (lane >= d) v += u;
+        }
+        if (i < end) block_counts[i] = run + v - c;
+        run += __shfl_sync(0xffffffffu, v, 31);
     }
     __syncthreads();
     // frame y starts at block y * blocks_per_frame
     const int base = offsets[f0];
     for (int y = t; y < n_frames; y += 1024) {
         const int first = (y + 1) * blocks_per_frame;
-        const int upto  = (first < n_blocks) ? block_counts[first] : partial[1023];
+        const int upto  = (first < n_blocks) ? block_counts[first] : total;
         offsets[f0 + y + 1] = base + upto;
     }
 }
