@@ -254,8 +254,9 @@ VM_API const char* vm_last_error(void);
  * ------------------------------------------------------------------------------------------------------------------ */
 typedef struct vm_hostmesh vm_hostmesh;
 
-/* model: "RING4" "RING6" "RING8" "XYGRID4" "XYGRID6" "XYGRID8"; shape: "SPHERE" (a = radius), "CIRCLE" (a = radius),
- * "CYLINDER" (a = radius, b = height). */
+/* model: "RING4" "RING6" "RING8", "XYGRID4" "XYGRID6" "XYGRID8", "XMGRID4" "XMGRID6" "XMGRID8", "NMGRID4" "NMGRID6"
+ * "NMGRID8" (every model of cpp/visualmesh/model/); shape: "SPHERE" (a = radius), "CIRCLE" (a = radius), "CYLINDER"
+ * (a = radius, b = height). */
 VM_API vm_status vm_hostmesh_create(const char* model,
                              const char* shape,
                              float shape_a,

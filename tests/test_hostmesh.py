@@ -88,6 +88,9 @@ def test_visualmesh_height_picks_the_nearest_table():
     W.MeshSpec("XYGRID8", "CIRCLE", 0.1, 0.0, 1.0, 2.0, 8.0),
     W.MeshSpec("XMGRID6", "SPHERE", 0.1, 0.0, 1.0, 2.0, 8.0),
     W.MeshSpec("XMGRID4", "CIRCLE", 0.1, 0.0, 0.7, 2.0, 6.0),
+    W.MeshSpec("NMGRID6", "SPHERE", 0.1, 0.0, 1.0, 2.0, 8.0),
+    W.MeshSpec("NMGRID4", "CIRCLE", 0.1, 0.0, 0.7, 2.0, 6.0),
+    W.MeshSpec("NMGRID8", "CYLINDER", 0.2, 1.8, 1.0, 2.0, 8.0),
 ], ids=lambda s: f"{s.model}-{s.shape}")
 def test_tables_and_lookup_match_the_compiled_reference(spec):
     ref, own = R.RefMesh(spec), Mesh.from_spec(spec)

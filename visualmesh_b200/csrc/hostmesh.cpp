@@ -5,7 +5,7 @@
 // that cannot instantiate those templates. It restates, in single precision with the host libm and the same
 // standard-library algorithms (so the same permutations), what the reference does once per camera height:
 //   model generation   cpp/visualmesh/model/ring_base.hpp:53-115, ring{4,6,8}.hpp, grid_base.hpp:78-144,
-//                      xygrid_map.hpp:40-48, xmgrid_map.hpp:42-50, polar_map.hpp:41-72
+//                      xygrid_map.hpp:40-48, xmgrid_map.hpp:42-50, nmgrid_map.hpp:30-127, polar_map.hpp:41-72
 //   shapes             cpp/visualmesh/geometry/Sphere.hpp:55-134, Circle.hpp:64-139, plus a Cylinder
 //   BSP construction   cpp/visualmesh/mesh.hpp:97-248, :425-467
 //   per-frame lookup   cpp/visualmesh/mesh.hpp:265-406, :499-595
@@ -40,6 +40,14 @@ namespace host {
                 case SPHERE: return -std::atan(std::sinh(n * std::log1p(-2.0f * r / h)));  // Sphere.hpp:75-77
                 case CIRCLE: return std::atan((2.0f * n * r) / h);                           // Circle.hpp:64-66
                 default: return std::atan((2.0f * n * r) / (h - half));
+            }
+        }
+        // n(phi, h): the inverse of phi - how many objects are stacked up to that angle
+        float n(float phi, float h) const {
+            switch (kind) {
+                case SPHERE: return std::asinh(std::tan(-phi)) / std::log1p(-2.0f * r / h);  // Sphere.hpp:79-81
+                case CIRCLE: return (h * std::tan(phi)) / (2.0f * r);                          // Circle.hpp:82-84
+                default: return ((h - half) * std::tan(phi)) / (2.0f * r);
             }
         }
         // height of the object's centre above the observation plane
@@ -134,10 +142,48 @@ namespace host {
     }
 
     // ---- grid models ---------------------------------------------------------------------------------------------
-    enum class GridMap { XY, XM };
+    enum class GridMap { XY, XM, NM };
+
+    // nmgrid_map.hpp:30-62: the point on the observation plane when the plane through the first axis stands at height
+    // h_n, and the second coordinate that point would have
+    static v3 nm_xyz(const Shape& shape, float h, float n, float h_n) {
+        const float c = shape.c();
+        const float x = (h_n - c) * std::tan(shape.phi(n, h_n));
+        const float y = std::sqrt((h_n - c) * (h_n - c) - (h - c) * (h - c));
+        return v3{{x, y, c - h}};
+    }
+    static float nm_guess_m(const Shape& shape, float h, float n, float h_n) {
+        const float c     = shape.c();
+        const v3 v        = nm_xyz(shape, h, n, h_n);
+        const float h_m   = std::sqrt(v[0] * v[0] + v[2] * v[2]) + c;
+        const float phi_m = std::acos(std::sqrt((v[0] * v[0] + v[2] * v[2]) / (v[0] * v[0] + v[1] * v[1] + v[2] * v[2])));
+        return shape.n(phi_m, h_m);
+    }
+    // nmgrid_map.hpp:91-127: bisection on the height of the first axis' plane until the second coordinate fits; it ends
+    // when the interval cannot be halved any more in float
+    static v3 nm_map(const Shape& shape, float h, const v2& nm) {
+        const float n = std::abs(nm[0]);
+        const float m = std::abs(nm[1]);
+        const float c = shape.c();
+        float lo      = h;
+        float hi      = (h - c) / std::cos(shape.phi(m, h)) + c;
+        float h_n     = (lo + hi) * 0.5f;
+        while (true) {
+            if (h_n == lo || h_n == hi) break;
+            const float m_g = nm_guess_m(shape, h, n, h_n);
+            (m_g > m ? hi : lo) = h_n;
+            if (h_n == (lo + hi) * 0.5f) break;
+            h_n = (lo + hi) * 0.5f;
+        }
+        v3 vec = nm_xyz(shape, h, n, h_n);
+        vec[0] *= nm[0] >= 0 ? 1 : -1;
+        vec[1] *= nm[1] >= 0 ? 1 : -1;
+        return vec;
+    }
 
     // xygrid_map.hpp:40-48, xmgrid_map.hpp:42-50
     static v3 grid_map(GridMap map, const Shape& shape, float h, const v2& nm) {
+        if (map == GridMap::NM) return nm_map(shape, h, nm);
         const float phi_x = shape.phi(nm[0], h);
         const float x     = (h - shape.c()) * std::tan(phi_x);
         float y;
@@ -476,8 +522,12 @@ vm_status vm_hostmesh_create(const char* model, const char* shape, float a, floa
             N     = m[6] - '0';
             nodes = generate_grid(GridMap::XM, N, sh, h, k, max_distance);
         }
+        else if (m == "NMGRID4" || m == "NMGRID6" || m == "NMGRID8") {
+            N     = m[6] - '0';
+            nodes = generate_grid(GridMap::NM, N, sh, h, k, max_distance);
+        }
         else {
-            vm_set_last_error_("unknown model (RING4/6/8, XYGRID4/6/8, XMGRID4/6/8)");
+            vm_set_last_error_("unknown model (RING4/6/8, XYGRID4/6/8, XMGRID4/6/8, NMGRID4/6/8)");
             return VM_ERR_INVALID_ARGUMENT;
         }
         std::unique_ptr<vm_hostmesh> hm(new vm_hostmesh());
