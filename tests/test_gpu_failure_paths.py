@@ -162,3 +162,16 @@ def test_mesh_of_another_engine_is_refused():
     assert P.compare(a.run_prepared(prepared).frame(0), fr, case.lens.dimensions).ok
     a.close()
     b.close()
+
+
+def test_nvtx_ranges_do_not_change_results():
+    """VMCUDA_NVTX=1 wraps every launch and every batch in an NVTX range; with no profiler attached the ranges are
+    no-ops and the results are those of an engine without them."""
+    case = G.Case("ring6_equisolid_rgba")
+    fr = case.frames[0]
+    engine = _engine_with_env(case.network, VMCUDA_NVTX=1)
+    mesh = Mesh.from_arrays(case.rays, case.nbrs, case.bsp)
+    for _ in range(2):
+        out = engine.run_batch([FrameInput(mesh, fr["Hoc"], case.lens, fr["image"], case.format, None)]).frame(0)
+        assert P.compare(out, fr, case.lens.dimensions).ok
+    engine.close()

@@ -6,6 +6,7 @@
 // kernels of another and the device-to-host copy of a third overlap.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <algorithm>
 #include <cmath>
@@ -192,12 +193,16 @@ struct vm_engine {
     cudaEvent_t ev_batch_start = nullptr;  // the start-of-batch clears (offsets[0], abort flag) are done
     cudaEvent_t ev_batch_done  = nullptr;  // everything of the batch, the abort flag's copy included, has finished
     bool blocking_sync         = false;    // host waits sleep instead of spinning
+    bool nvtx                  = false;    // NVTX ranges around every kernel launch and batch (VMCUDA_NVTX=1)
 };
 
 namespace vm {
 
+// A stage is one kernel launch. With VMCUDA_NVTX=1 every launch sits in an NVTX range of the stage's name (the header-only
+// NVTX does nothing unless a profiler is attached); with stage timing on, between two CUDA events.
 static void begin_stage(vm_engine* e, cudaStream_t s, const char* name) {
     ++e->launches;
+    if (e->nvtx) nvtxRangePushA(name);
     if (!e->timing) return;
     while (e->event_pool.size() < e->events_used + 2) {
         cudaEvent_t ev;
@@ -210,6 +215,7 @@ static void begin_stage(vm_engine* e, cudaStream_t s, const char* name) {
     e->timers.push_back(t);
 }
 static void end_stage(vm_engine* e, cudaStream_t s) {
+    if (e->nvtx) nvtxRangePop();
     if (!e->timing) return;
     VM_CUDA(cudaEventRecord(e->timers.back().stop, s));
 }
@@ -593,6 +599,15 @@ static vm_status run_batch(vm_engine* e, const vm_frame* frames, int32_t n_frame
     }
     std::memset(out, 0, sizeof(*out));
     if (n_frames == 0) return VM_OK;
+    struct BatchRange {  // one NVTX range per batch, closed on every way out
+        bool on;
+        explicit BatchRange(bool enabled) : on(enabled) {
+            if (on) nvtxRangePushA("vm_run_batch");
+        }
+        ~BatchRange() {
+            if (on) nvtxRangePop();
+        }
+    } batch_range(e->nvtx);
 
     // validation, before any device work - the reference throws from inside the call for the same conditions
     bool classify = frames[0].image != nullptr && !e->layers.empty();
@@ -827,6 +842,7 @@ vm_status vm_engine_create(int device, const vm_layer* layers, const int32_t* la
         if (const char* v = std::getenv("VMCUDA_TC_NO_SPLIT")) e->tc_no_split = std::atoi(v) != 0;
         if (const char* v = std::getenv("VMCUDA_STAGED")) e->staged = std::atoi(v) != 0;
         if (const char* v = std::getenv("VMCUDA_BLOCKING_SYNC")) e->blocking_sync = std::atoi(v) != 0;
+        if (const char* v = std::getenv("VMCUDA_NVTX")) e->nvtx = std::atoi(v) != 0;
         if (const char* v = std::getenv("VMCUDA_LANES")) e->n_lanes = std::min(MAX_LANES, std::max(1, std::atoi(v)));
         for (int l = 0; l < MAX_LANES; ++l) {
             Lane& lane = e->lanes[l];
