@@ -42,6 +42,9 @@ import numpy as np  # noqa: E402
 from visualmesh_b200 import sharding  # noqa: E402
 from visualmesh_b200 import workloads as W  # noqa: E402
 
+# VMCUDA_BLOCKING_SYNC exported by the caller applies to every engine; otherwise the bench decides per engine (Arm)
+USER_SET_BLOCKING_SYNC = "VMCUDA_BLOCKING_SYNC" in os.environ
+
 # DRAM traffic per row of the dominant kernels from their ncu captures (dram__bytes_read + dram__bytes_write over the
 # rows of the captured launch); traffic grows in proportion to the rows, so it is scaled to the bench's launches.
 NCU_TRAFFIC_BYTES_PER_ROW = {
@@ -214,11 +217,23 @@ class Arm:
     """One workload on one GPU: its frames once in pinned host memory (the end-to-end mode) and once in HBM (the
     device-resident mode), an engine, and the two timed loops."""
 
-    def __init__(self, wl, frames, device, instances):
+    def __init__(self, wl, frames, device, instances, sleepy_e2e=False):
         import torch
         from visualmesh_b200.engine import Engine, FrameInput, Mesh
         self.torch, self.wl, self.frames, self.device = torch, wl, frames, device
-        self.engine = Engine(wl.network, device=device)
+
+        def make_engine(sleepy):
+            # an engine reads VMCUDA_BLOCKING_SYNC when it is created; a value the user exported is left alone
+            if USER_SET_BLOCKING_SYNC:
+                return Engine(wl.network, device=device)
+            os.environ["VMCUDA_BLOCKING_SYNC"] = "1" if sleepy else "0"
+            try:
+                return Engine(wl.network, device=device)
+            finally:
+                os.environ.pop("VMCUDA_BLOCKING_SYNC", None)
+
+        # the device-resident loop has one host thread per GPU: its waits always spin
+        self.engine = make_engine(False)
         self.meshes = {}
         for fr in frames:
             if fr.mesh.key() not in self.meshes:
@@ -241,7 +256,9 @@ class Arm:
         # their steps back to back - the reference's own advice for its GPU engines (readme/inference.md:70-77,
         # example/benchmark.cpp:86-101, :133): while one instance waits for its last copies another uploads
         n_inst = max(1, min(instances, len(frames)))
-        self.engines = [self.engine] + [Engine(wl.network, device=device) for _ in range(n_inst - 1)]
+        # (with many ranks on a box with few cores these threads' waits sleep instead of spinning: engines of their own)
+        self.engines = ([make_engine(True) for _ in range(n_inst)] if sleepy_e2e
+                        else [self.engine] + [make_engine(False) for _ in range(n_inst - 1)])
         parts = [sharding.shard(self.host_frames, i, n_inst) for i in range(n_inst)]
         self.batches = [eng.prepare_batch(part) for eng, part in zip(self.engines, parts)]
         self.d2h_bytes = 0
@@ -434,8 +451,7 @@ def run_ours(args, rank, world, local_rank):
         raise SystemExit("bench.py needs a CUDA device: the engine has no CPU fallback")
     # several ranks' engine threads on a box with few cores: let the waits sleep instead of spinning
     cores = os.cpu_count() or 1
-    if "VMCUDA_BLOCKING_SYNC" not in os.environ and world * (args.instances + 1) > cores // 2:
-        os.environ["VMCUDA_BLOCKING_SYNC"] = "1"
+    sleepy_e2e = (os.environ.get("VMCUDA_BLOCKING_SYNC") == "1") if USER_SET_BLOCKING_SYNC else world * (args.instances + 1) > cores // 2
     torch.cuda.set_device(local_rank)
     dist = None
     if world > 1:
@@ -460,7 +476,7 @@ def run_ours(args, rank, world, local_rank):
     per_gpu = args.frames
     wl = W.config(args.config, seed=args.seed, n_frames=per_gpu * world)
     frames = sharding.shard(wl.frames, rank, world)  # rank r takes its contiguous slice of the seeded stream
-    arm = Arm(wl, frames, local_rank, args.instances)
+    arm = Arm(wl, frames, local_rank, args.instances, sleepy_e2e)
 
     # ---- device-resident arm: `value`, per-kernel times for the roofline ----
     warm = max(args.warmup, 3)
@@ -526,7 +542,7 @@ def run_ours(args, rank, world, local_rank):
     if args.stream_frames > 0 and not args.quick:
         wl4 = W.config(4, seed=args.seed, n_frames=args.stream_frames)
         mine = sharding.round_robin(wl4.frames, rank, world)
-        arm4 = Arm(wl4, mine, local_rank, args.instances)
+        arm4 = Arm(wl4, mine, local_rank, args.instances, sleepy_e2e)
         arm4.warm(2)
         barrier()
         d_ms, pts4, _, _ = arm4.run_device(2)
@@ -588,7 +604,7 @@ def run_ours(args, rank, world, local_rank):
         e2e = {"value": e2e_value, "unit": "frames/s", "h2d_bytes_per_step": h2d_bytes * world,
                "d2h_bytes_per_step": d2h_bytes * world, "ms_per_step": 1e3 * e2e_elapsed / args.steps,
                "engine_instances": args.instances,
-               "host_waits": "sleeping" if os.environ.get("VMCUDA_BLOCKING_SYNC") == "1" else "spinning"}
+               "host_waits": "sleeping" if sleepy_e2e else "spinning"}
         if copy_s:
             e2e["copy_bound_ms"] = 1e3 * copy_s
             e2e["frac_of_bound"] = copy_s / (e2e_elapsed / args.steps)
