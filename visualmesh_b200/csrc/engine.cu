@@ -556,12 +556,13 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
                 const int cls = format_class(frames[f].format);
                 packed4 &= cls == FMT_RGBA || cls == FMT_BGRA;
             }
+            const dim3 gs((max_rows + ROW_THREADS * SAMPLE_ROWS - 1) / (ROW_THREADS * SAMPLE_ROWS), nf);
             if (packed4) {
-                k_sample<true><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_px.p,
+                k_sample<true><<<gs, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_px.p,
                                                          reinterpret_cast<float4*>(lane.d_feat[0].p));
             }
             else {
-                k_sample<false><<<g, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_px.p,
+                k_sample<false><<<gs, ROW_THREADS, 0, s>>>(lane.d_frames.p, e->d_offsets.p, f0, e->d_px.p,
                                                           reinterpret_cast<float4*>(lane.d_feat[0].p));
             }
             VM_CUDA(cudaGetLastError());

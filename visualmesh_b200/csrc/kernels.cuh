@@ -20,6 +20,7 @@ namespace vm {
 
 constexpr int SELECT_THREADS = 256;
 constexpr int ROW_THREADS    = 256;
+constexpr int SAMPLE_ROWS    = 2;    // points per thread of k_sample
 
 enum : uint8_t { BSP_DESCEND = 0, BSP_INSIDE = 1, BSP_OUTSIDE = 2 };
 
@@ -292,21 +293,34 @@ __global__ void __launch_bounds__(ROW_THREADS) k_sample(const FrameParams* __res
                                                         int32_t f0,
                                                         const float2* __restrict__ out_px,
                                                         float4* __restrict__ features) {
+    // a thread samples SAMPLE_ROWS points, ROW_THREADS apart: the pixel coordinates of all of them are loaded before
+    // the first texel, so that many independent chains of two dependent loads are in flight per thread
     const FrameParams& p = frames[blockIdx.y];
     const int frame      = f0 + blockIdx.y;
     const int start      = offsets[frame];
     const int n          = offsets[frame + 1] - start;
-    const int i          = blockIdx.x * ROW_THREADS + threadIdx.x;
-    if (i > n) return;
-    const int local_row = start - offsets[f0] + blockIdx.y + i;
-    float4 v            = make_float4(-1.0f, -1.0f, -1.0f, -1.0f);
-    if (i < n) {
-        if (PACKED4) { v = interpolate_packed4(out_px[start + i], p.image, p.dims[0], p.dims[1], p.format == fcc('B', 'G', 'R', 'A')); }
-        else {
-            v = interpolate(out_px[start + i], p.image, p.dims[0], p.dims[1], format_class(p.format));
-        }
+    const int first      = blockIdx.x * (ROW_THREADS * SAMPLE_ROWS) + threadIdx.x;
+    if (first > n) return;
+    const int row0 = start - offsets[f0] + blockIdx.y;
+    float2 px[SAMPLE_ROWS];
+#pragma unroll
+    for (int q = 0; q < SAMPLE_ROWS; ++q) {
+        const int i = first + q * ROW_THREADS;
+        px[q]       = (i < n) ? out_px[start + i] : make_float2(0.0f, 0.0f);
     }
-    features[local_row] = v;
+#pragma unroll
+    for (int q = 0; q < SAMPLE_ROWS; ++q) {
+        const int i = first + q * ROW_THREADS;
+        if (i > n) break;
+        float4 v = make_float4(-1.0f, -1.0f, -1.0f, -1.0f);
+        if (i < n) {
+            if (PACKED4) { v = interpolate_packed4(px[q], p.image, p.dims[0], p.dims[1], p.format == fcc('B', 'G', 'R', 'A')); }
+            else {
+                v = interpolate(px[q], p.image, p.dims[0], p.dims[1], format_class(p.format));
+            }
+        }
+        features[row0 + i] = v;
+    }
 }
 
 // The same sampler on a flat list of pixel coordinates (stand-alone stage for unit parity tests).
