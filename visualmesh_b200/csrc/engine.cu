@@ -524,10 +524,10 @@ static void enqueue_chunk(vm_engine* e, Lane& lane, Lane* prev, const vm_frame* 
     VM_CUDA(cudaMemcpyAsync(e->h_offsets.p + f0 + 1, e->d_offsets.p + f0 + 1, sizeof(int32_t) * nf, cudaMemcpyDeviceToHost, s));
     VM_CUDA(cudaEventRecord(lane.ev_offsets, s));
     {
-        dim3 g(blocks_per_frame, nf);
+        dim3 g((blocks_per_frame + SCATTER_UNITS - 1) / SCATTER_UNITS, nf);
         begin_stage(e, s, "scatter_compact");
-        k_scatter<<<g, SELECT_THREADS, 0, s>>>(lane.d_frames.p, lane.d_cand_px.p, lane.d_cand_node.p, lane.d_block_counts.p,
-                                               e->d_offsets.p, f0, e->d_px.p, e->d_gi.p, lane.d_node_rank.p);
+        k_scatter<SCATTER_UNITS><<<g, SELECT_THREADS, 0, s>>>(lane.d_frames.p, lane.d_cand_px.p, lane.d_cand_node.p, lane.d_block_counts.p,
+                                                              blocks_per_frame, e->d_offsets.p, f0, e->d_px.p, e->d_gi.p, lane.d_node_rank.p);
         VM_CUDA(cudaGetLastError());
         end_stage(e, s);
     }
@@ -1292,7 +1292,7 @@ vm_status vm_project_static(vm_engine* e,
         k_bsp_state<<<dim3((mesh->n_bsp + SELECT_THREADS - 1) / SELECT_THREADS, 1), SELECT_THREADS, 0, s>>>(d_frame, d_state);
         k_select<<<dim3(blocks, 1), SELECT_THREADS, 0, s>>>(d_frame, d_state, d_cand_px, d_cand_node, d_blocks, d_cells + 2);
         k_scan<<<1, 1024, 0, s>>>(d_blocks, blocks, blocks, 1, d_cells, 0);
-        k_scatter<<<dim3(blocks, 1), SELECT_THREADS, 0, s>>>(d_frame, d_cand_px, d_cand_node, d_blocks, d_cells, 0,
+        k_scatter<1><<<dim3(blocks, 1), SELECT_THREADS, 0, s>>>(d_frame, d_cand_px, d_cand_node, d_blocks, blocks, d_cells, 0,
                                                              reinterpret_cast<float2*>(d_px), d_gi, d_rank);
         dim3 g((mesh->n_nodes + 1 + ROW_THREADS - 1) / ROW_THREADS, 1);
         const st::PlanOut no_plan{nullptr, nullptr, nullptr};

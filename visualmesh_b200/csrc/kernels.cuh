@@ -20,6 +20,7 @@ namespace vm {
 
 constexpr int SELECT_THREADS = 256;
 constexpr int ROW_THREADS    = 256;
+constexpr int SCATTER_UNITS  = 4;    // runs of SELECT_THREADS candidates per block of k_scatter
 constexpr int SAMPLE_ROWS    = 2;    // points per thread of k_sample
 
 enum : uint8_t { BSP_DESCEND = 0, BSP_INSIDE = 1, BSP_OUTSIDE = 2 };
@@ -203,38 +204,55 @@ __global__ void __launch_bounds__(1024) k_scan(int32_t* __restrict__ block_count
 // (cpp/visualmesh/engine/cpu/engine.hpp:110-120). Also fills the node -> local index table that k_remap reads in
 // place of the reference's r_lookup (engine.hpp:128-131); with device lookup every entry is written, with host
 // ranges the table was cleared to -1 beforehand.
+template <int UNITS>
 __global__ void __launch_bounds__(SELECT_THREADS) k_scatter(const FrameParams* __restrict__ frames,
                                                             const float2* __restrict__ cand_px,
                                                             const int32_t* __restrict__ cand_node,
                                                             const int32_t* __restrict__ block_offsets,
+                                                            int32_t blocks_per_frame,
                                                             const int32_t* __restrict__ offsets,
                                                             int32_t f0,
                                                             float2* __restrict__ out_px,
                                                             int32_t* __restrict__ out_gi,
                                                             int32_t* __restrict__ node_rank) {
-    __shared__ int32_t warp_counts[SELECT_THREADS / 32];
+    // a block compacts UNITS runs of SELECT_THREADS candidates (the unit k_select counted and k_scan scanned); their
+    // loads are issued together
+    __shared__ int32_t warp_counts[UNITS][SELECT_THREADS / 32];
     const FrameParams& p = frames[blockIdx.y];
-    const int c          = blockIdx.x * SELECT_THREADS + threadIdx.x;
-    int g                = -1;
-    if (c < p.n_candidates) g = cand_node[p.cand_off + c];
-    const bool keep      = g >= 0;
-    const unsigned mask  = __ballot_sync(0xffffffffu, keep);
     const int lane       = threadIdx.x & 31;
     const int warp       = threadIdx.x >> 5;
-    if (lane == 0) warp_counts[warp] = __popc(mask);
-    __syncthreads();
-    int before = 0;
-    for (int w = 0; w < warp; ++w) before += warp_counts[w];
-    const int in_chunk = block_offsets[blockIdx.y * gridDim.x + blockIdx.x] + before + __popc(mask & ((1u << lane) - 1u));
-    const int frame    = f0 + blockIdx.y;
-    if (keep) {
-        const int o  = offsets[f0] + in_chunk;
-        out_px[o]    = cand_px[p.cand_off + c];
-        out_gi[o]    = g;
-        node_rank[p.node_off + g] = o - offsets[frame];
+    const int frame      = f0 + blockIdx.y;
+    int c[UNITS], g[UNITS];
+    unsigned mask[UNITS];
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        c[u] = (blockIdx.x * UNITS + u) * SELECT_THREADS + threadIdx.x;
+        g[u] = (c[u] < p.n_candidates) ? cand_node[p.cand_off + c[u]] : -1;
     }
-    else if (c < p.n_candidates && p.ranges == nullptr) {
-        node_rank[p.node_off + c] = -1;
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        mask[u] = __ballot_sync(0xffffffffu, g[u] >= 0);
+        if (lane == 0) warp_counts[u][warp] = __popc(mask[u]);
+    }
+    __syncthreads();
+    const int chunk_base = offsets[f0];
+    const int frame_base = offsets[frame];
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        const int unit = blockIdx.x * UNITS + u;
+        if (unit >= blocks_per_frame) break;
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_counts[u][w];
+        const int in_chunk = block_offsets[blockIdx.y * blocks_per_frame + unit] + before + __popc(mask[u] & ((1u << lane) - 1u));
+        if (g[u] >= 0) {
+            const int o  = chunk_base + in_chunk;
+            out_px[o]    = cand_px[p.cand_off + c[u]];
+            out_gi[o]    = g[u];
+            node_rank[p.node_off + g[u]] = o - frame_base;
+        }
+        else if (c[u] < p.n_candidates && p.ranges == nullptr) {
+            node_rank[p.node_off + c[u]] = -1;
+        }
     }
 }
 
