@@ -152,8 +152,10 @@ __device__ __forceinline__ void ffma2(unsigned long long& acc, unsigned long lon
 
 // Accumulators live as pairs of adjacent output columns, each weight pair is one 64-bit constant load shared by the R
 // rows, each input value is duplicated into a pair once per row and k.
+// The narrow 8-channel layers wait on their gather: six blocks of 256 threads per SM (42 registers) instead of five
+// measured 102 -> 98 us on the 8 -> 3 layer over 4.4 M rows, eight (32 registers) spill. 0 = no bound for the others.
 template <int CIN, int COUT, int R, int WMAX, int T = CONV_THREADS, int NS = 0>
-__global__ void __launch_bounds__(T) k_graph_conv_cw(const ConvArgs a, const __grid_constant__ ConvWeights<WMAX> wp) {
+__global__ void __launch_bounds__(T, (CIN == 8 && COUT <= 8 && T == 256) ? 6 : 0) k_graph_conv_cw(const ConvArgs a, const __grid_constant__ ConvWeights<WMAX> wp) {
     static_assert(CIN % 4 == 0, "vector loads of the input rows");
     constexpr int COUTP = (COUT + 3) & ~3;
     const int frame_in_chunk = blockIdx.y;
